@@ -1,0 +1,162 @@
+// Embedding gather, RMSNorm, rotary encoding with cache write, residual helpers.
+//
+// These replace the reference's embedding_lookup_kernel, rmsnorm_kernel,
+// generate_rope_frequencies_kernel + rope_split_half_kernel and the two
+// device-to-device copies that append K and V (src/cuda/gemm_cuda.cu:172-202,
+// 239-274, 286-295; src/models/transformer_block.cpp:484-509), for a batch of
+// tokens instead of one, and without --use_fast_math: 1/sqrtf and a host-built
+// cos/sin table stand where the reference has rsqrtf and fast sincosf.
+#include "common.cuh"
+
+namespace skv {
+
+// ---------------------------------------------------------------------------
+// x[t, :] = table[ids[t], :] widened to float.  An id outside the vocabulary
+// (hosts check before launching) writes zeros and raises the flag.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int hidden, int vocab, int* __restrict__ flag) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* row_out = out + (size_t)t * hidden;
+    if (id < 0 || id >= vocab) {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_out[c] = 0.0f;
+        if (threadIdx.x == 0 && flag) atomicOr(flag, 1);
+        return;
+    }
+    const T* row = table + (size_t)id * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_out[c] = to_float(row[c]);
+}
+
+// ---------------------------------------------------------------------------
+// y[r, :] = x[src(r), :] * (1 / sqrt(mean(x^2) + eps)) * gamma, sums in float.
+// The multiplication order is the reference's (src/layers/rmsnorm.cpp:91-93).
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                               float eps, T* __restrict__ out, const int* __restrict__ rows,
+                               int hidden) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const float* row = x + (size_t)src * hidden;
+    float partial = 0.0f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = row[c];
+        partial = fmaf(v, v, partial);
+    }
+    const float mean_square = block_sum(partial, scratch) / (float)hidden;
+    const float inverse_rms = 1.0f / sqrtf(mean_square + eps);
+    T* row_out = out + (size_t)r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        row_out[c] = from_float<T>(row[c] * inverse_rms * gamma[c]);
+}
+
+// ---------------------------------------------------------------------------
+// One token per block.  Rotates every query head and key head with split-half
+// pairs (i, i + head_dim/2) (src/layers/attention.cpp:96-135), writes queries
+// in the compute dtype, and writes the rotated keys and the values into the
+// token's place in the paged cache: block = table[seq][pos / block_size],
+// row = pos % block_size of tile [kv_head][block_size][head_dim].
+template <typename T>
+__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2* __restrict__ cos_sin,
+                                     const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                     const int* __restrict__ block_table, int table_width,
+                                     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                     int num_heads, int num_kv_heads, int head_dim, int block_size,
+                                     int write_kv) {
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1;
+    const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
+    const int pos = positions[t];
+    const float* src = qkv + (size_t)t * (q_dim + 2 * kv_dim);
+    const float2* angles = cos_sin ? cos_sin + (size_t)pos * half : nullptr;
+    size_t tile_base = 0;
+    if (write_kv) {
+        const int seq = token_seq[t];
+        const int block = block_table[(size_t)seq * table_width + pos / block_size];
+        tile_base = ((size_t)block * num_kv_heads * block_size + (pos % block_size)) * head_dim;
+    }
+    const int rotary_heads = num_heads + (write_kv ? num_kv_heads : 0);
+    for (int idx = threadIdx.x; idx < rotary_heads * half; idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const float* x = src + (size_t)head * head_dim;     // key heads follow the query heads
+        float c = 1.0f, s = 0.0f;
+        if (angles) { const float2 a = angles[i]; c = a.x; s = a.y; }
+        const float x1 = x[i], x2 = x[i + half];
+        const float r1 = x1 * c - x2 * s;
+        const float r2 = x1 * s + x2 * c;
+        if (head < num_heads) {
+            T* dst = q_out + (size_t)t * q_dim + (size_t)head * head_dim;
+            dst[i] = from_float<T>(r1);
+            dst[i + half] = from_float<T>(r2);
+        } else {
+            const int g = head - num_heads;
+            T* dst = k_cache + tile_base + (size_t)g * block_size * head_dim;
+            dst[i] = from_float<T>(r1);
+            dst[i + half] = from_float<T>(r2);
+        }
+    }
+    if (write_kv) {
+        const float* v = src + q_dim + kv_dim;
+        for (int idx = threadIdx.x; idx < kv_dim; idx += blockDim.x) {
+            const int g = idx / head_dim, d = idx - g * head_dim;
+            v_cache[tile_base + (size_t)g * block_size * head_dim + d] = from_float<T>(v[idx]);
+        }
+    }
+}
+
+// out[i] += in[i]  (float residual stream; used by parts that have no fused epilogue)
+__global__ void add_inplace_kernel(float* __restrict__ out, const float* __restrict__ in, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] += in[i];
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+SKV_EXPORT const char* skv_last_error() { return error_buffer(); }
+SKV_EXPORT int skv_library_dtype() { return SKV_DTYPE; }
+SKV_EXPORT int skv_library_head_dim() { return SKV_HEAD_DIM; }
+
+SKV_EXPORT int skv_embed(const void* table, const int* ids, float* out, int n_tokens, int hidden,
+                         int vocab, int* flag, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0) return fail("skv_embed", "hidden and vocab must be positive");
+    const int threads = hidden >= 1024 ? 256 : 128;
+    embed_kernel<skv_t><<<n_tokens, threads, 0, stream>>>((const skv_t*)table, ids, out, hidden, vocab, flag);
+    return check_launch("skv_embed");
+}
+
+SKV_EXPORT int skv_rmsnorm(const float* x, const float* gamma, float eps, void* out, const int* rows,
+                           int n_rows, int hidden, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (hidden <= 0) return fail("skv_rmsnorm", "hidden must be positive");
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    rmsnorm_kernel<skv_t><<<n_rows, threads, 0, stream>>>(x, gamma, eps, (skv_t*)out, rows, hidden);
+    return check_launch("skv_rmsnorm");
+}
+
+SKV_EXPORT int skv_rope_kv_write(const float* qkv, const float* cos_sin, const int* positions,
+                                 const int* token_seq, const int* block_table, int table_width,
+                                 void* q_out, void* k_cache, void* v_cache, int n_tokens,
+                                 int num_heads, int num_kv_heads, int head_dim, int block_size,
+                                 int write_kv, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (head_dim <= 0 || (head_dim & 1)) return fail("skv_rope_kv_write", "head_dim must be positive and even");
+    if (num_heads <= 0 || num_kv_heads <= 0 || block_size <= 0)
+        return fail("skv_rope_kv_write", "head counts and block_size must be positive");
+    rope_kv_write_kernel<skv_t><<<n_tokens, 128, 0, stream>>>(
+        qkv, (const float2*)cos_sin, positions, token_seq, block_table, table_width, (skv_t*)q_out,
+        (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv);
+    return check_launch("skv_rope_kv_write");
+}
+
+SKV_EXPORT int skv_add_inplace(float* out, const float* in, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    long long blocks = (n + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    add_inplace_kernel<<<(int)blocks, threads, 0, stream>>>(out, in, (size_t)n);
+    return check_launch("skv_add_inplace");
+}

@@ -1,0 +1,267 @@
+// Linear layers: out = A[M,K] . W[N,K]^T with a fused epilogue.
+//
+// W keeps the checkpoint's [out, in] rows (K contiguous), as the reference's
+// GPU path does (src/generation/generator.cpp:311-319).  These kernels replace
+// its warp-per-output GEMV and 32x32 tile GEMM (src/cuda/gemm_cuda.cu:445-608)
+// and the separate add and SwiGLU kernels that follow them (:221-231, 276-284).
+//
+// Epilogues (`mode`):
+//   0 STORE      out[M,N] in the compute dtype
+//   1 STORE_F32  out[M,N] float
+//   2 ADD_F32    out[M,N] float += result          (residual sum in float)
+//   3 GATED      W rows come in tiles of 16: rows 0-7 of a tile are gate rows
+//                8t..8t+7, rows 8-15 the matching up rows; out[M,N/2] =
+//                act(gate) * up in the compute dtype
+//
+// float build: a true 32-bit FMA tile kernel (no tensor cores, no TF32).
+// bfloat16 build: a weight-streaming kernel for any M that keeps 16 weight rows
+// per block and feeds tokens in groups of 8 through mma.sync m16n8k16 with float
+// accumulation.  Each lane loads 16 bytes (8 consecutive k) of a weight row and of
+// a token row and issues two MMAs on them; the k order inside an MMA is permuted
+// the same way for both operands, which leaves the dot products unchanged.
+#include "common.cuh"
+
+namespace skv {
+
+enum { MODE_STORE = 0, MODE_STORE_F32 = 1, MODE_ADD_F32 = 2, MODE_GATED = 3 };
+enum { ACT_SILU = 0 };
+
+__device__ __forceinline__ float activate(float g, int act) {
+    // silu(g) = g * sigmoid(g); the two-branch sigmoid of the reference's CPU
+    // block (src/models/transformer_block.cpp:315-323) avoids overflow of exp.
+    (void)act;
+    const float sig = g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
+    return g * sig;
+}
+
+template <typename T>
+__device__ __forceinline__ void epilogue_store(void* out, int mode, int M, int N, int m, int n, float v) {
+    if (m >= M || n >= N) return;
+    const size_t at = (size_t)m * N + n;
+    if (mode == MODE_STORE) ((T*)out)[at] = from_float<T>(v);
+    else if (mode == MODE_STORE_F32) ((float*)out)[at] = v;
+    else ((float*)out)[at] += v;
+}
+
+#if SKV_DTYPE == SKV_F32
+// ---------------------------------------------------------------------------
+// 64x64 output tile, K in steps of 16, 256 threads, 4 tokens x 4 columns each.
+// A thread's columns are {2j, 2j+1, 2j+8, 2j+9} of one 16-column group so that a
+// gate column and its up column meet in one thread.
+constexpr int FBM = 64, FBN = 64, FBK = 16;
+
+__global__ void __launch_bounds__(256)
+linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void* __restrict__ out,
+                  int M, int N, int K, int mode, int act) {
+    __shared__ float As[FBK][FBM + 4];
+    __shared__ float Ws[FBK][FBN + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * FBM, n0 = blockIdx.x * FBN;
+    const int group = tx >> 2, j = tx & 3;
+    int cols[4] = {16 * group + 2 * j, 16 * group + 2 * j + 1, 16 * group + 2 * j + 8, 16 * group + 2 * j + 9};
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += FBK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = tid + i * 256;
+            const int row = e >> 4, k = e & 15;
+            const int gm = m0 + row, gn = n0 + row, gk = k0 + k;
+            As[k][row] = (gm < M && gk < K) ? A[(size_t)gm * K + gk] : 0.0f;
+            Ws[k][row] = (gn < N && gk < K) ? W[(size_t)gn * K + gk] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < FBK; ++k) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) w[c] = Ws[k][cols[c]];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[i][c] = fmaf(a[i], w[c], acc[i][c]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (mode == MODE_GATED) {
+            if (m >= M) continue;
+            const int half_n = N >> 1;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int n = n0 + cols[c];            // a gate row of W; its up row is n + 8
+                if (n >= N) continue;
+                const int o = ((n >> 4) << 3) + (n & 7);
+                if (o < half_n)
+                    ((float*)out)[(size_t)m * half_n + o] = activate(acc[i][c], act) * acc[i][c + 2];
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) epilogue_store<float>(out, mode, M, N, m, n0 + cols[c], acc[i][c]);
+        }
+    }
+}
+
+static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+                         cudaStream_t stream) {
+    dim3 grid((N + FBN - 1) / FBN, (M + FBM - 1) / FBM);
+    linear_f32_kernel<<<grid, 256, 0, stream>>>((const float*)a, (const float*)w, out, M, N, K, mode, act);
+    return check_launch("skv_linear(float)");
+}
+
+#else  // bfloat16
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool STREAM>
+__device__ __forceinline__ uint4 load_weight16(const uint4* p) {
+    return STREAM ? __ldcs(p) : __ldg(p);
+}
+
+// One block owns 16 rows of W and one chunk of 8*TG tokens.  Its warps take the
+// 32-wide k steps round robin, then their partial tiles are summed in shared
+// memory in warp order (a fixed order: results do not depend on timing).
+template <int TG, bool STREAM>
+__global__ void __launch_bounds__(256)
+skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
+                          void* __restrict__ out, int M, int N, int K, int mode, int act) {
+    extern __shared__ float red[];                 // [warps][16][8*TG + 1]
+    constexpr int COLS = 8 * TG, PITCH = COLS + 1;
+    const int warps = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tig = lane & 3;
+    const int n0 = blockIdx.x * 16, m0 = blockIdx.y * COLS;
+    const int steps = (K + 31) >> 5;
+
+    const int row_a = min(n0 + g, N - 1), row_b = min(n0 + g + 8, N - 1);
+    const bool has_a = n0 + g < N, has_b = n0 + g + 8 < N;
+    const __nv_bfloat16* wa_ptr = W + (size_t)row_a * K + tig * 8;
+    const __nv_bfloat16* wb_ptr = W + (size_t)row_b * K + tig * 8;
+    const __nv_bfloat16* x_ptr[TG];
+    bool has_x[TG];
+#pragma unroll
+    for (int t = 0; t < TG; ++t) {
+        const int m = m0 + t * 8 + g;
+        has_x[t] = m < M;
+        x_ptr[t] = X + (size_t)min(m, M - 1) * K + tig * 8;
+    }
+    float acc[TG][4];
+#pragma unroll
+    for (int t = 0; t < TG; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f; }
+
+    constexpr int U = 4;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int s0 = warp; s0 < steps; s0 += warps * U) {
+        uint4 wa[U], wb[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (s0 + u * warps) << 5;
+            const bool live = (s0 + u * warps) < steps && (k + tig * 8) < K;
+            wa[u] = (live && has_a) ? load_weight16<STREAM>((const uint4*)(wa_ptr + k)) : zero;
+            wb[u] = (live && has_b) ? load_weight16<STREAM>((const uint4*)(wb_ptr + k)) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (s0 + u * warps) << 5;
+            const bool live = (s0 + u * warps) < steps && (k + tig * 8) < K;
+#pragma unroll
+            for (int t = 0; t < TG; ++t) {
+                const uint4 xv = (live && has_x[t]) ? *(const uint4*)(x_ptr[t] + k) : zero;
+                mma_bf16_16816(acc[t], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
+                mma_bf16_16816(acc[t], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
+            }
+        }
+    }
+    float* mine = red + (size_t)warp * 16 * PITCH;
+#pragma unroll
+    for (int t = 0; t < TG; ++t) {
+        mine[g * PITCH + t * 8 + 2 * tig] = acc[t][0];
+        mine[g * PITCH + t * 8 + 2 * tig + 1] = acc[t][1];
+        mine[(g + 8) * PITCH + t * 8 + 2 * tig] = acc[t][2];
+        mine[(g + 8) * PITCH + t * 8 + 2 * tig + 1] = acc[t][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * COLS; idx += blockDim.x) {
+        const int r = idx & 15, m = idx >> 4;
+        float sum = 0.0f;
+        for (int w = 0; w < warps; ++w) sum += red[((size_t)w * 16 + r) * PITCH + m];
+        red[(size_t)r * PITCH + m] = sum;          // warp 0's tile becomes the total
+        // (each (r, m) is read and written by this thread only)
+    }
+    __syncthreads();
+    if (mode == MODE_GATED) {
+        const int half_n = N >> 1;
+        for (int idx = threadIdx.x; idx < 8 * COLS; idx += blockDim.x) {
+            const int r = idx & 7, m = idx >> 3;
+            const int o = (n0 >> 1) + r, gm = m0 + m;
+            if (gm < M && o < half_n) {
+                const float gate = red[(size_t)r * PITCH + m], up = red[(size_t)(r + 8) * PITCH + m];
+                ((__nv_bfloat16*)out)[(size_t)gm * half_n + o] = __float2bfloat16_rn(activate(gate, act) * up);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 16 * COLS; idx += blockDim.x) {
+            const int r = idx & 15, m = idx >> 4;
+            epilogue_store<__nv_bfloat16>(out, mode, M, N, m0 + m, n0 + r, red[(size_t)r * PITCH + m]);
+        }
+    }
+}
+
+template <int TG>
+static int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+                         cudaStream_t stream) {
+    const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
+    const int steps = (K + 31) / 32;
+    // Enough warps to keep loads in flight on 148 SMs, never more than k steps.
+    int warps = 8;
+    if ((long long)row_tiles * chunks >= 148 * 4) warps = 4;
+    while (warps > 1 && warps > steps) warps >>= 1;
+    const size_t smem = (size_t)warps * 16 * (8 * TG + 1) * sizeof(float);
+    dim3 grid(row_tiles, chunks);
+    if (chunks == 1)
+        skinny_linear_bf16_kernel<TG, true><<<grid, warps * 32, smem, stream>>>(
+            (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K, mode, act);
+    else
+        skinny_linear_bf16_kernel<TG, false><<<grid, warps * 32, smem, stream>>>(
+            (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K, mode, act);
+    return check_launch("skv_linear(bfloat16)");
+}
+
+static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+                         cudaStream_t stream) {
+    if (K % 8 != 0)
+        return fail("skv_linear(bfloat16)", "the inner size must be a multiple of 8 (16-byte rows)");
+    if (((uintptr_t)a | (uintptr_t)w) & 15)
+        return fail("skv_linear(bfloat16)", "operands must be 16-byte aligned");
+    if (M <= 8) return launch_skinny<1>(a, w, out, M, N, K, mode, act, stream);
+    if (M <= 16) return launch_skinny<2>(a, w, out, M, N, K, mode, act, stream);
+    if (M <= 32) return launch_skinny<4>(a, w, out, M, N, K, mode, act, stream);
+    return launch_skinny<8>(a, w, out, M, N, K, mode, act, stream);
+}
+#endif
+
+}  // namespace skv
+
+using namespace skv;
+
+SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+                          cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (N <= 0 || K <= 0) return fail("skv_linear", "N and K must be positive");
+    if (mode < 0 || mode > 3) return fail("skv_linear", "unknown epilogue mode");
+    if (mode == MODE_GATED && N % 16 != 0)
+        return fail("skv_linear", "a gated weight must have a multiple of 16 rows (gate/up tiles of 8)");
+    if (act != ACT_SILU) return fail("skv_linear", "unknown activation");
+    return launch_linear(a, w, out, M, N, K, mode, act, stream);
+}

@@ -1,0 +1,188 @@
+"""The engine: a model, its cache, and the one step function everything uses.
+
+``step`` takes a batch of sequences, each with its next tokens (a whole prompt,
+a piece of one, or a single decoded token) and the places whose logits are
+wanted; it runs only those tokens, as one packed batch without padding, against
+what earlier steps left in the cache, and returns the logits.  The reference's
+counterpart handles one token of one sequence per call
+(``src/generation/generator.cpp:571-614``, ``src/models/transformer_block.cpp:348-351``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from .. import models as _models  # noqa: F401  (registers the architectures)
+from .. import ops as _ops
+from ..cache import CacheFull, KVCache
+from ..config import EngineConfig, load_config
+from ..config.registry import resolve_architecture
+from ..parts.base import Runtime, StepBatch
+from ..parts.spec import ModelSpec
+from ..parts.workspace import Workspace
+from ..weights.loader import load_checkpoint
+from .model import Model, cache_requests, default_head_dim, expected_tensors
+
+
+@dataclass
+class StepEntry:
+    """One sequence's share of a step: its slot, its next tokens, and the
+    indices among these tokens whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepError(ValueError):
+    pass
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], config: EngineConfig,
+                 kernel_loader=None, verbose: bool = True):
+        self.spec = spec
+        self.config = config
+        if kernel_loader is None:
+            self.device = _ops.require_cuda(config.device)
+            kernel_loader = lambda dtype, head_dim: _ops.kernels_for(dtype, head_dim, verbose=verbose)
+        else:                                   # tests hand in a stand-in for the kernels
+            self.device = torch.device(config.device)
+        self.workspace = Workspace(self.device)
+        self.rt = Runtime(config.dtype, self.device, self.workspace, kernel_loader, default_head_dim(spec))
+        self.model = Model(spec, self.rt)
+        self.model.bind(tensors)
+        self.cache = KVCache(cache_requests(spec), config.num_blocks, config.block_size, config.slots,
+                             config.dtype, self.device)
+        self._pinned: Optional[torch.Tensor] = None
+        self._meta: Optional[torch.Tensor] = None
+
+    # ---- construction ----------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir, config: EngineConfig, verbose: bool = True) -> "Engine":
+        """Open a folder with ``config.json`` and ``model.safetensors``; the
+        architecture named in ``config.json`` chooses the model."""
+        arch, model_config = load_config(model_dir)
+        spec = arch.build_spec(model_config)
+        expected = {name: request.shape for name, request in expected_tensors(spec).items()}
+        tensors = load_checkpoint(model_dir, expected, spec.ignorable)
+        engine = cls(spec, tensors, config, verbose=verbose)
+        engine.model_config = model_config
+        return engine
+
+    @classmethod
+    def from_config(cls, model_config, config: EngineConfig, seed: int = 0,
+                    stored_dtype: Optional[torch.dtype] = None, verbose: bool = True) -> "Engine":
+        """Random weights for ``model_config`` made in memory (no folder)."""
+        from ..weights.random_init import random_tensors
+        spec = resolve_architecture(model_config.architecture).build_spec(model_config)
+        tensors = random_tensors(expected_tensors(spec), seed, dtype=stored_dtype or config.dtype)
+        engine = cls(spec, tensors, config, verbose=verbose)
+        engine.model_config = model_config
+        return engine
+
+    # ---- sequences ---------------------------------------------------------------
+    def open_sequence(self) -> int:
+        return self.cache.acquire()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    # ---- the step ------------------------------------------------------------------
+    def _metadata(self, count: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self._meta is None or self._meta.numel() < count:
+            capacity = max(count, 4096, 2 * (self._meta.numel() if self._meta is not None else 0))
+            self._meta = torch.empty(capacity, dtype=torch.int32, device=self.device)
+            pin = self.device.type == "cuda"
+            self._pinned = torch.empty(capacity, dtype=torch.int32, pin_memory=pin)
+        return self._pinned, self._meta
+
+    def prepare(self, entries: Sequence[StepEntry]):
+        """Check a step, reserve its cache blocks, and upload its metadata.
+        Returns ``(StepBatch, want_rows, n_want)``; nothing has run yet."""
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        vocab = self.spec.vocab_size
+        slots = [e.slot for e in entries]
+        if len(set(slots)) != len(slots):
+            raise StepError("a sequence appears twice in one step")
+        if len(entries) > self.config.slots:
+            raise StepError(f"{len(entries)} sequences in one step; the engine holds {self.config.slots}")
+        q_lens, ctx_before, wanted = [], [], {}
+        for e in entries:
+            if e.slot not in self.cache.sequences:
+                raise StepError(f"slot {e.slot} is not open")
+            if len(e.tokens) == 0:
+                raise StepError(f"slot {e.slot}: a step needs at least one token per sequence")
+            for token in e.tokens:
+                if not (0 <= int(token) < vocab):
+                    raise StepError(f"slot {e.slot}: token id {token} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not (0 <= int(w) < len(e.tokens)):
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside this step's {len(e.tokens)} tokens")
+            before = self.cache.length(e.slot)
+            q_lens.append(len(e.tokens))
+            ctx_before.append(before)
+            wanted[e.slot] = before + len(e.tokens)
+        self.cache.reserve(wanted)              # CacheFull leaves everything as it was
+
+        n, total = len(entries), sum(q_lens)
+        max_ctx = max(wanted.values())
+        width = -(-max_ctx // self.cache.block_size)
+        token_ids, positions, token_seq, want_rows, cu_q = [], [], [], [], [0]
+        for index, e in enumerate(entries):
+            base = cu_q[-1]
+            token_ids.extend(int(t) for t in e.tokens)
+            positions.extend(range(ctx_before[index], ctx_before[index] + q_lens[index]))
+            token_seq.extend([index] * q_lens[index])
+            want_rows.extend(base + int(w) for w in e.want)
+            cu_q.append(base + q_lens[index])
+        ctx_after = [wanted[s] for s in slots]
+        tables = [self.cache.block_table_rows(g.index, slots, width) for g in self.cache.groups]
+        flat: List[int] = []
+        offsets = {}
+        for name, values in (("token_ids", token_ids), ("positions", positions), ("token_seq", token_seq),
+                             ("cu_q", cu_q), ("ctx_after", ctx_after), ("slot_ids", slots),
+                             ("want_rows", want_rows)):
+            offsets[name] = (len(flat), len(values))
+            flat.extend(values)
+        for g, rows in enumerate(tables):
+            offsets[("table", g)] = (len(flat), n * width)
+            for row in rows:
+                flat.extend(row)
+        pinned, meta = self._metadata(len(flat))
+        pinned[:len(flat)] = torch.tensor(flat, dtype=torch.int32)
+        meta[:len(flat)].copy_(pinned[:len(flat)], non_blocking=True)
+
+        def view(key):
+            start, count = offsets[key]
+            return meta[start:start + count]
+
+        step = StepBatch(
+            n_seqs=n, n_tokens=total, slots=slots, q_lens=q_lens, ctx_before=ctx_before,
+            max_q_len=max(q_lens), max_ctx=max_ctx,
+            token_ids=view("token_ids"), positions=view("positions"), token_seq=view("token_seq"),
+            cu_q=view("cu_q"), ctx_after=view("ctx_after"), slot_ids=view("slot_ids"),
+            block_tables={g: view(("table", g)).view(n, width) for g in range(len(tables))},
+            cache=self.cache)
+        return step, (view("want_rows") if want_rows else None), len(want_rows)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one step.  Returns float32 logits ``[wanted, vocab]`` on the device,
+        in the order of the entries and of their ``want`` (``None`` when nothing
+        is wanted).  The tensor is scratch memory: use or copy it before the next step."""
+        step, want_rows, n_want = self.prepare(entries)
+        logits = self.model.forward(step, want_rows, n_want)
+        for e in entries:
+            self.cache.advance(e.slot, self.cache.length(e.slot) + len(e.tokens))
+        return logits
+
+    def check_flags(self) -> None:
+        """Raise if a kernel flagged bad input since the last check (reads one word from the device)."""
+        flags = int(self.model.flags.item())
+        if flags:
+            self.model.flags.zero_()
+            raise StepError(f"device flags raised: {flags:#x} (1: token id outside the vocabulary, "
+                            "2: non-finite logits)")

@@ -1,0 +1,124 @@
+"""A model built from a ``ModelSpec``: embedding, layers in schedule order, final norm, head.
+
+One forward pass of a step: gather embeddings into the float32 residual stream,
+run every schedule entry's layer, then normalise only the rows whose logits are
+wanted and multiply them with the head (the reference likewise computes the
+final norm and the head on the last position only, ``src/generation/generator.cpp:
+691-715``).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional
+
+import torch
+
+from .. import ops as _ops
+from ..parts.base import CacheRequest, Runtime, StepBatch, TensorRequest
+from ..parts.block import Layer
+from ..parts.registry import part_class
+from ..parts.spec import ModelSpec
+
+
+def expected_tensors(spec: ModelSpec) -> Dict[str, TensorRequest]:
+    """Every checkpoint tensor the model needs, by name, with its shape."""
+    found: Dict[str, TensorRequest] = {}
+
+    def add(requests: Mapping[str, TensorRequest]):
+        for name, request in requests.items():
+            if name in found and tuple(found[name].shape) != tuple(request.shape):
+                raise ValueError(f"tensor {name} is requested with two shapes: "
+                                 f"{found[name].shape} and {request.shape}")
+            found.setdefault(name, request)
+
+    add({spec.embedding.weight: TensorRequest((spec.embedding.vocab_size, spec.embedding.hidden_size))})
+    for layer in spec.layers:
+        add(part_class("norm", layer.mixer_norm.kind).expected_tensors(layer.mixer_norm))
+        add(part_class("mixer", layer.mixer.kind).expected_tensors(layer.mixer))
+        add(part_class("norm", layer.ffn_norm.kind).expected_tensors(layer.ffn_norm))
+        add(part_class("ffn", layer.ffn.kind).expected_tensors(layer.ffn))
+    add(part_class("norm", spec.final_norm.kind).expected_tensors(spec.final_norm))
+    add({spec.head.weight: TensorRequest((spec.head.vocab_size, spec.head.hidden_size))})
+    return found
+
+
+def cache_requests(spec: ModelSpec) -> List[CacheRequest]:
+    """What each cache entry must hold, from the mixer of the run that writes it."""
+    requests: List[Optional[CacheRequest]] = [None] * spec.num_cache_entries()
+    for entry in spec.schedule:
+        if not (0 <= entry.layer < len(spec.layers)):
+            raise ValueError(f"schedule names layer {entry.layer}; the model has {len(spec.layers)}")
+        if entry.writes_cache:
+            if requests[entry.cache] is not None:
+                raise ValueError(f"cache entry {entry.cache} is written by two runs")
+            mixer = spec.layers[entry.layer].mixer
+            requests[entry.cache] = part_class("mixer", mixer.kind).cache_request(mixer)
+    for index, request in enumerate(requests):
+        if request is None:
+            raise ValueError(f"cache entry {index} is read but no run writes it")
+    return requests
+
+
+def default_head_dim(spec: ModelSpec) -> int:
+    for layer in spec.layers:
+        head_dim = getattr(layer.mixer, "head_dim", None)
+        if head_dim:
+            return head_dim
+    return 64       # no part needs a head size: any build of the library will do
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, runtime: Runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.layers = [Layer(layer_spec, runtime) for layer_spec in spec.layers]
+        self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, runtime)
+        self.embedding = None
+        self.head = None
+        # Raised by kernels: bit 0 = token id outside the vocabulary.
+        self.flags = torch.zeros(1, dtype=torch.int32, device=runtime.device)
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        uploaded: Dict[str, torch.Tensor] = {}
+
+        def table(name):
+            if name not in uploaded:
+                uploaded[name] = self.rt.upload(tensors[name])
+            return uploaded[name]
+
+        self.embedding = table(self.spec.embedding.weight)
+        self.head = table(self.spec.head.weight)          # the same tensor when tied
+        for layer in self.layers:
+            for part in layer.parts():
+                part.bind(tensors)
+        self.final_norm.bind(tensors)
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights one decode step reads (each matrix once; one embedding row per token is left out)."""
+        seen, total = set(), 0
+        tensors = [self.head, self.final_norm.gamma] if hasattr(self.final_norm, "gamma") else [self.head]
+        for layer in self.layers:
+            for part in layer.parts():
+                for value in vars(part).values():
+                    if isinstance(value, torch.Tensor):
+                        tensors.append(value)
+        for tensor in tensors:
+            if tensor.data_ptr() not in seen:
+                seen.add(tensor.data_ptr())
+                total += tensor.numel() * tensor.element_size()
+        return total
+
+    def forward(self, step: StepBatch, want_rows: Optional[torch.Tensor], n_want: int):
+        """Run the step's tokens; return float32 logits ``[n_want, vocab]`` (a view
+        of scratch memory that the next step overwrites) or ``None``."""
+        rt, spec = self.rt, self.spec
+        ops = rt.kernels()
+        x = rt.workspace.get("residual", (step.n_tokens, spec.hidden_size), torch.float32)
+        ops.embed(self.embedding, step.token_ids, x, self.flags)
+        for entry in spec.schedule:
+            self.layers[entry.layer].forward(step, x, entry)
+        if n_want == 0:
+            return None
+        y = self.final_norm.forward(x, rows=want_rows, name="final_normed")
+        logits = rt.workspace.get("logits", (n_want, spec.vocab_size), torch.float32)
+        ops.linear(y, self.head, logits, _ops.MODE_STORE_F32)
+        return logits

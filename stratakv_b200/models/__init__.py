@@ -1,0 +1,2 @@
+"""Architectures.  Importing this package registers every one of them."""
+from . import llama  # noqa: F401

@@ -1,0 +1,173 @@
+"""The kernel library as Python calls: loads the compiled .so and checks arguments.
+
+There is one backend: hand-written CUDA for sm_100a, loaded through ctypes.
+If it cannot be compiled or loaded, or no CUDA device is present, the calls
+raise; nothing falls back to the CPU or to library model code.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .csrc.build import BuildError, build_library
+
+MODE_STORE, MODE_STORE_F32, MODE_ADD_F32, MODE_GATED = 0, 1, 2, 3
+ACTIVATIONS = {"silu": 0, "swish": 0}
+_DTYPE_NAMES = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(tensor: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Kernels:
+    """The kernels of one (compute dtype, head size) library."""
+
+    def __init__(self, dtype: torch.dtype, head_dim: int, verbose: bool = True):
+        if dtype not in _DTYPE_NAMES:
+            raise KernelError(f"no kernels for dtype {dtype}")
+        self.dtype = dtype
+        self.head_dim = head_dim
+        try:
+            self.path = build_library(_DTYPE_NAMES[dtype], head_dim, verbose=verbose)
+        except BuildError as error:
+            raise KernelError(str(error)) from None
+        try:
+            self.lib = ctypes.CDLL(str(self.path))
+        except OSError as error:
+            raise KernelError(f"cannot load {self.path}: {error}") from None
+        self.lib.skv_last_error.restype = ctypes.c_char_p
+        if self.lib.skv_library_head_dim() != head_dim:
+            raise KernelError(f"{self.path} was built for another head size")
+
+    # ---- helpers -----------------------------------------------------------
+    def _check(self, code: int, name: str) -> None:
+        if code != 0:
+            raise KernelError(f"{name}: {self.lib.skv_last_error().decode()}")
+
+    def _want(self, tensor: torch.Tensor, dtype, name: str) -> None:
+        if not tensor.is_cuda:
+            raise KernelError(f"{name} must be a CUDA tensor: the kernels run on the GPU only")
+        if tensor.dtype != dtype:
+            raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+        if not tensor.is_contiguous():
+            raise KernelError(f"{name} must be contiguous")
+
+    # ---- kernels -------------------------------------------------------------
+    def embed(self, table, ids, out, flag=None):
+        """out[t, :] = table[ids[t], :] as float32."""
+        self._want(table, self.dtype, "table"); self._want(ids, torch.int32, "ids")
+        self._want(out, torch.float32, "out")
+        n, hidden = out.shape
+        vocab = table.shape[0]
+        if table.shape[1] != hidden or ids.numel() != n:
+            raise KernelError("embed: shapes do not agree")
+        self._check(self.lib.skv_embed(_ptr(table), _ptr(ids), _ptr(out), n, hidden, vocab, _ptr(flag), _stream()),
+                    "embed")
+
+    def rmsnorm(self, x, gamma, eps: float, out, rows=None):
+        """out[r, :] = rmsnorm(x[rows[r] or r, :]) * gamma, in the compute dtype."""
+        self._want(x, torch.float32, "x"); self._want(gamma, torch.float32, "gamma")
+        self._want(out, self.dtype, "out")
+        hidden = x.shape[-1]
+        n_rows = out.shape[0]
+        if gamma.numel() != hidden or out.shape[-1] != hidden:
+            raise KernelError("rmsnorm: shapes do not agree")
+        if rows is not None:
+            self._want(rows, torch.int32, "rows")
+            if rows.numel() != n_rows:
+                raise KernelError("rmsnorm: one output row per index is needed")
+        elif x.shape[0] != n_rows:
+            raise KernelError("rmsnorm: shapes do not agree")
+        self._check(self.lib.skv_rmsnorm(_ptr(x), _ptr(gamma), ctypes.c_float(eps), _ptr(out), _ptr(rows),
+                                         n_rows, hidden, _stream()), "rmsnorm")
+
+    def linear(self, a, w, out, mode: int = MODE_STORE, activation: str = "silu"):
+        """out = a[M,K] . w[N,K]^T with the epilogue ``mode``."""
+        self._want(a, self.dtype, "a"); self._want(w, self.dtype, "w")
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K:
+            raise KernelError(f"linear: inner sizes differ ({K} and {w.shape[1]})")
+        out_cols = N // 2 if mode == MODE_GATED else N
+        out_dtype = self.dtype if mode in (MODE_STORE, MODE_GATED) else torch.float32
+        self._want(out, out_dtype, "out")
+        if tuple(out.shape) != (M, out_cols):
+            raise KernelError(f"linear: out must be [{M}, {out_cols}], got {list(out.shape)}")
+        if activation not in ACTIVATIONS:
+            raise KernelError(f"linear: unknown activation '{activation}'")
+        self._check(self.lib.skv_linear(_ptr(a), _ptr(w), _ptr(out), M, N, K, mode, ACTIVATIONS[activation],
+                                        _stream()), "linear")
+
+    def rope_kv_write(self, qkv, cos_sin, positions, token_seq, block_table, q_out, k_cache, v_cache,
+                      num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, write_kv: bool):
+        self._want(qkv, torch.float32, "qkv"); self._want(q_out, self.dtype, "q_out")
+        self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
+        self._want(block_table, torch.int32, "block_table")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
+        if cos_sin is not None:
+            self._want(cos_sin, torch.float32, "cos_sin")
+        n = qkv.shape[0]
+        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+            raise KernelError("rope_kv_write: qkv width does not match the head counts")
+        self._check(self.lib.skv_rope_kv_write(
+            _ptr(qkv), _ptr(cos_sin), _ptr(positions), _ptr(token_seq), _ptr(block_table),
+            block_table.shape[1], _ptr(q_out), _ptr(k_cache), _ptr(v_cache), n, num_heads, num_kv_heads,
+            head_dim, block_size, int(bool(write_kv)), _stream()), "rope_kv_write")
+
+    def attention(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads: int,
+                  num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0):
+        self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
+        self._want(block_table, torch.int32, "block_table")
+        self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
+        n = q.shape[0]
+        self._check(self.lib.skv_attention(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(positions),
+            _ptr(token_seq), _ptr(out), n, num_heads, num_kv_heads, head_dim, block_size,
+            ctypes.c_float(scale), window, _stream()), "attention")
+
+    def add_inplace(self, out, other):
+        self._want(out, torch.float32, "out"); self._want(other, torch.float32, "other")
+        if out.numel() != other.numel():
+            raise KernelError("add_inplace: sizes differ")
+        self._check(self.lib.skv_add_inplace(_ptr(out), _ptr(other), ctypes.c_longlong(out.numel()), _stream()),
+                    "add_inplace")
+
+    def argmax(self, logits, out, flag=None):
+        self._want(logits, torch.float32, "logits"); self._want(out, torch.int32, "out")
+        rows, vocab = logits.shape
+        self._check(self.lib.skv_argmax(_ptr(logits), _ptr(out), rows, vocab, _ptr(flag), _stream()), "argmax")
+
+
+_LOADED: Dict[Tuple[torch.dtype, int], Kernels] = {}
+
+
+def kernels_for(dtype: torch.dtype, head_dim: int, verbose: bool = True) -> Kernels:
+    key = (dtype, head_dim)
+    if key not in _LOADED:
+        _LOADED[key] = Kernels(dtype, head_dim, verbose=verbose)
+    return _LOADED[key]
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise KernelError(f"device {device}: this library runs on CUDA devices only")
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is available: this library has no CPU path")
+    major, minor = torch.cuda.get_device_capability(device)
+    if major != 10:
+        raise KernelError(f"device {device} has compute capability {major}.{minor}; "
+                          "the kernels are built for sm_100a only")
+    return device

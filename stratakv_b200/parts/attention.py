@@ -1,0 +1,71 @@
+"""Causal grouped-query attention over the paged cache.
+
+``q, k, v = h.Wq^T, h.Wk^T, h.Wv^T`` (no bias); rotary encoding on every query
+and key head before the key is cached; scores ``(q.k) * scale`` over the
+sequence's own earlier positions and the token itself; softmax and the weighted
+sum of values in float; ``x += ctx.Wo^T`` (``src/layers/attention.cpp:153-342``,
+``src/models/transformer_block.cpp:301-309``).  The three projections are one
+matrix ``[q | k | v]`` here, and the residual sum is the epilogue of the output
+projection.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops as _ops
+from .base import CacheRequest, Mixer, TensorRequest
+from .registry import part_class, register_mixer
+
+
+class PagedAttention(Mixer):
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        if spec.num_heads % spec.num_kv_heads != 0:
+            raise ValueError("attention: heads must be a multiple of kv heads")
+        if spec.head_dim % 16 != 0:
+            raise ValueError(f"attention: head size {spec.head_dim} is not supported "
+                             "(the kernels take multiples of 16)")
+        self.q_dim = spec.num_heads * spec.head_dim
+        self.kv_dim = spec.num_kv_heads * spec.head_dim
+        position_spec = spec.position
+        kind = position_spec.kind if position_spec is not None else "none"
+        self.position = part_class("position", kind)(position_spec, runtime)
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        q_dim, kv_dim = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        return {spec.q_weight: TensorRequest((q_dim, spec.hidden_size)),
+                spec.k_weight: TensorRequest((kv_dim, spec.hidden_size)),
+                spec.v_weight: TensorRequest((kv_dim, spec.hidden_size)),
+                spec.o_weight: TensorRequest((spec.hidden_size, q_dim))}
+
+    @classmethod
+    def cache_request(cls, spec):
+        kind = "kv_window" if spec.window > 0 else "kv"
+        return CacheRequest(kind, spec.num_kv_heads, spec.head_dim, spec.window)
+
+    def bind(self, tensors):
+        s = self.spec
+        parts = [self.rt.upload(tensors[name]) for name in (s.q_weight, s.k_weight, s.v_weight)]
+        self.w_qkv = torch.cat(parts, dim=0).contiguous()
+        del parts
+        self.w_o = self.rt.upload(tensors[s.o_weight])
+
+    def forward(self, step, h, x, cache_entry, writes_cache=True):
+        s, rt = self.spec, self.rt
+        ops = rt.kernels(s.head_dim)
+        n = h.shape[0]
+        qkv = rt.workspace.get("qkv", (n, self.q_dim + 2 * self.kv_dim), torch.float32)
+        ops.linear(h, self.w_qkv, qkv, _ops.MODE_STORE_F32)
+        k_cache, v_cache = step.cache.entry_kv(cache_entry)
+        table = step.block_tables[step.cache.entry_group_index(cache_entry)]
+        q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
+        self.position.rotate_and_store(step, qkv, q, k_cache, v_cache, table, s.num_heads, s.num_kv_heads,
+                                       s.head_dim, step.cache.block_size, writes_cache)
+        ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
+        ops.attention(q, k_cache, v_cache, table, step.positions, step.token_seq, ctx, s.num_heads,
+                      s.num_kv_heads, s.head_dim, step.cache.block_size, s.scale, s.window)
+        ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32)
+
+
+register_mixer("attention", PagedAttention)

@@ -1,0 +1,138 @@
+"""Interfaces every part implements, and what a part is handed when it runs.
+
+A part is built from its spec and a ``Runtime`` (compute dtype, device, the
+kernel library), says which checkpoint tensors it needs, receives them once in
+``bind`` and then runs inside steps.  The residual stream ``x`` is a float32
+``[tokens, hidden]`` tensor that mixers and feed-forwards add their result to
+(the reference keeps the same stream in FP32, ``src/models/transformer_block.cpp:
+301-331``); norms read it and emit the compute dtype.
+
+Mixer:        ``forward(step, h, x, cache_entry, writes_cache)``  ->  ``x += mix(h)``
+Feed-forward: ``forward(step, h, x)``                            ->  ``x += ffn(h)``
+Norm:         ``forward(x, rows=None)``                          ->  ``h`` (compute dtype)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class TensorRequest:
+    """A checkpoint tensor a part needs.  ``init`` tells the random-weights mode
+    how to fill it: ``normal`` is N(0, std), ``around_one`` is 1 + N(0, std)."""
+    shape: Tuple[int, ...]
+    init: str = "normal"
+
+
+@dataclass(frozen=True)
+class CacheRequest:
+    """What one run of a mixer needs from the cache.
+
+    ``kind`` ``"kv"`` keeps every key and value; ``"kv_window"`` needs only the
+    last ``window``; ``"none"`` keeps no keys.  ``state_bytes`` is fixed-size
+    per-sequence state (zeroed when a sequence takes its slot).  Runs whose
+    requests are equal share one group of storage."""
+    kind: str = "none"
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    window: int = 0
+    state_bytes: int = 0
+
+    def group_key(self):
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window)
+
+
+class Runtime:
+    """What parts share: compute dtype, device, scratch buffers and the kernel library."""
+
+    def __init__(self, dtype: torch.dtype, device, workspace, kernel_loader, default_head_dim: int):
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.workspace = workspace
+        self._kernel_loader = kernel_loader          # (dtype, head_dim) -> kernels object
+        self.default_head_dim = default_head_dim
+
+    def kernels(self, head_dim: Optional[int] = None):
+        """The kernel library; attention parts name their head size, others take any build."""
+        return self._kernel_loader(self.dtype, head_dim or self.default_head_dim)
+
+    def upload(self, tensor: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """Copy a checkpoint tensor to the device in ``dtype`` (default: the
+        compute dtype).  float32 -> bfloat16 rounds to nearest even; the
+        reference truncates (``src/cuda/gemm_cuda.cu:74-83``)."""
+        return tensor.to(device=self.device, dtype=dtype or self.dtype).contiguous()
+
+
+@dataclass
+class StepBatch:
+    """One step's tokens: several sequences, each with ``q_len`` new tokens
+    after ``ctx_before`` cached ones, packed back to back without padding.
+
+    Host lists describe the batch; the device tensors are what kernels read.
+    ``block_tables[g]`` is ``[n_seqs, width]`` int32 for cache group ``g``.
+    """
+    n_seqs: int
+    n_tokens: int
+    slots: List[int]
+    q_lens: List[int]
+    ctx_before: List[int]
+    max_q_len: int
+    max_ctx: int                       # longest context after this step
+    token_ids: torch.Tensor            # [n_tokens] int32
+    positions: torch.Tensor            # [n_tokens] int32, absolute position of each token
+    token_seq: torch.Tensor            # [n_tokens] int32, which sequence of the batch
+    cu_q: torch.Tensor                 # [n_seqs + 1] int32
+    ctx_after: torch.Tensor            # [n_seqs] int32
+    slot_ids: torch.Tensor             # [n_seqs] int32
+    block_tables: Dict[int, torch.Tensor]
+    cache: Any                         # cache.KVCache
+    scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+    @property
+    def is_decode(self) -> bool:
+        return self.max_q_len == 1
+
+
+class Part:
+    role = "part"
+
+    def __init__(self, spec, runtime: Runtime):
+        self.spec = spec
+        self.rt = runtime
+
+    @classmethod
+    def expected_tensors(cls, spec) -> Dict[str, TensorRequest]:
+        return {}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Receive the checkpoint tensors named by ``expected_tensors`` (CPU, stored dtype)."""
+
+
+class Norm(Part):
+    role = "norm"
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    role = "mixer"
+
+    @classmethod
+    def cache_request(cls, spec) -> CacheRequest:
+        return CacheRequest()
+
+    def forward(self, step: StepBatch, h: torch.Tensor, x: torch.Tensor,
+                cache_entry: int, writes_cache: bool) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    role = "ffn"
+
+    def forward(self, step: StepBatch, h: torch.Tensor, x: torch.Tensor) -> None:
+        raise NotImplementedError

@@ -1,0 +1,69 @@
+"""Tiny configurations and small utilities shared by the tests."""
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+# Two tiny Llama configurations that differ in every size and option.
+TINY_A = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=176,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+              vocab_size=256, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=64,
+              tie_word_embeddings=False, eos_token_id=2, hidden_act="silu")
+TINY_B = dict(architectures=["LlamaForCausalLM"], hidden_size=96, intermediate_size=256,
+              num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=3, head_dim=16,
+              vocab_size=384, rms_norm_eps=1e-6, rope_theta=500000.0, max_position_embeddings=128,
+              tie_word_embeddings=True, eos_token_id=[5, 7], hidden_act="silu")
+# A third one with a head size that is not the hidden size over the heads, MHA, and an odd vocabulary.
+TINY_C = dict(architectures=["LlamaForCausalLM"], hidden_size=80, intermediate_size=104,
+              num_hidden_layers=1, num_attention_heads=3, num_key_value_heads=3, head_dim=32,
+              vocab_size=331, rms_norm_eps=3e-6, rope_theta=25000.0, max_position_embeddings=512,
+              tie_word_embeddings=False, hidden_act="silu")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def make_folder(folder, raw_config, seed, dtype=torch.float32):
+    from stratakv_b200.config import LlamaConfig
+    from stratakv_b200.weights import write_random_model
+    return write_random_model(folder, LlamaConfig.from_dict(raw_config), seed, dtype)
+
+
+def random_tokens(vocab, length, seed):
+    generator = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (length,), generator=generator).tolist()
+
+
+def run_trace(model_dir, dtype, steps, out_dir, max_tokens, timeout=600):
+    """Run bin/trace_run on ``steps`` (a list of dicts); returns {step: array [wanted, vocab]}."""
+    out_dir = Path(out_dir)
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    result = subprocess.run(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
+         "--out", str(out_dir), "--max-tokens", str(max_tokens)],
+        input=text, capture_output=True, text=True, timeout=timeout)
+    assert result.returncode == 0, result.stderr[-4000:]
+    done = [line for line in result.stdout.splitlines() if line.startswith("done ")]
+    assert [line.split()[1] for line in done] == [str(s["step"]) for s in steps], result.stdout
+    vocab = json.loads((Path(model_dir) / "config.json").read_text())["vocab_size"]
+    logits = {}
+    for s in steps:
+        wanted = sum(len(e.get("want", [])) for e in s["entries"])
+        path = out_dir / f"{s['step']}.f32"
+        if wanted:
+            logits[s["step"]] = np.fromfile(path, dtype="<f4").reshape(wanted, vocab)
+        else:
+            assert not path.exists()
+    return logits
+
+
+def tolerance(dtype):
+    """(rtol, atol) for logits of tiny random models against the plain float32 implementation."""
+    if dtype in ("float32", torch.float32):
+        return 1e-4, 2e-5
+    return 3e-2, 3e-2

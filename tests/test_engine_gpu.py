@@ -1,0 +1,136 @@
+"""The engine against the plain implementation: whole requests, the last 32 tokens one by
+one, and batches of unequal lengths whose shorter requests end earlier, one batch after
+another so that slots and blocks are used again; in float32 and in bfloat16."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+from helpers import TINY, make_folder, random_tokens, tolerance
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {name: make_folder(root / name, raw, seed=11 + i) for i, (name, raw) in enumerate(TINY.items())}
+
+
+@pytest.fixture(scope="module")
+def plain(folders):
+    cache = {}
+
+    def logits(name, tokens):
+        key = (name, tuple(tokens))
+        if key not in cache:
+            config, weights = plain_llama.load_folder(folders[name])
+            cache[key] = plain_llama.logits_of(config, weights, tokens).numpy()
+        return cache[key]
+    return logits
+
+
+def engine_for(folder, dtype, max_tokens=2048, block_size=64):
+    from stratakv_b200 import Engine, EngineConfig
+    return Engine.from_folder(folder, EngineConfig(max_tokens=max_tokens, dtype=dtype, block_size=block_size),
+                              verbose=False)
+
+
+def check(got, ref, dtype, what=""):
+    rtol, atol = tolerance(dtype)
+    got = got.detach().float().cpu().numpy() if isinstance(got, torch.Tensor) else got
+    np.testing.assert_allclose(got, ref, rtol=rtol, atol=atol, err_msg=what)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(TINY))
+def test_whole_requests(folders, plain, dtype, name):
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name], dtype)
+    vocab = TINY[name]["vocab_size"]
+    for length in (1, 2, 17, 64, 65, 150):
+        tokens = random_tokens(vocab, length, seed=length)
+        slot = engine.open_sequence()
+        got = engine.step([StepEntry(slot, tokens, list(range(length)))])
+        check(got, plain(name, tokens), dtype, f"{name} whole length {length}")
+        engine.close_sequence(slot)
+    assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(TINY))
+def test_last_32_tokens_one_by_one(folders, plain, dtype, name):
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name], dtype)
+    vocab = TINY[name]["vocab_size"]
+    for length in (33, 80, 131):
+        tokens = random_tokens(vocab, length, seed=100 + length)
+        ref = plain(name, tokens)
+        slot = engine.open_sequence()
+        head = length - 32
+        got = engine.step([StepEntry(slot, tokens[:head], [head - 1])])
+        check(got, ref[head - 1:head], dtype, f"{name} prefix of {length}")
+        for position in range(head, length):
+            got = engine.step([StepEntry(slot, [tokens[position]], [0])])
+            check(got, ref[position:position + 1], dtype, f"{name} length {length} position {position}")
+        engine.close_sequence(slot)
+    assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(TINY))
+def test_unequal_batches_with_slot_reuse(folders, plain, dtype, name):
+    """Batches start together with unequal prompts, decode together, and the shorter
+    requests leave earlier; the next batch takes the freed slots and blocks."""
+    from stratakv_b200 import StepEntry
+    engine = engine_for(folders[name], dtype, max_tokens=64 * 6, block_size=16)
+    vocab = TINY[name]["vocab_size"]
+    batches = [[(5, 8), (9, 3), (13, 12)], [(1, 12), (7, 1), (16, 5), (31, 9)], [(40, 2), (3, 30)]]
+    seed = 0
+    for batch in batches:
+        requests = []
+        for prompt_len, decode_len in batch:
+            seed += 1
+            tokens = random_tokens(vocab, prompt_len + decode_len, seed=seed)
+            requests.append(dict(tokens=tokens, prompt=prompt_len, total=prompt_len + decode_len,
+                                 slot=engine.open_sequence(), ref=plain(name, tokens)))
+        got = engine.step([StepEntry(r["slot"], r["tokens"][:r["prompt"]], [r["prompt"] - 1]) for r in requests])
+        check(got, np.stack([r["ref"][r["prompt"] - 1] for r in requests]), dtype, f"{name} prompts {batch}")
+        fed = {id(r): r["prompt"] for r in requests}
+        live = list(requests)
+        while live:
+            for r in [r for r in live if fed[id(r)] >= r["total"]]:
+                engine.close_sequence(r["slot"])
+                live.remove(r)
+            if not live:
+                break
+            got = engine.step([StepEntry(r["slot"], [r["tokens"][fed[id(r)]]], [0]) for r in live])
+            check(got, np.stack([r["ref"][fed[id(r)]] for r in live]), dtype,
+                  f"{name} decode at {[fed[id(r)] for r in live]}")
+            for r in live:
+                fed[id(r)] += 1
+        assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_and_company_change_nothing(folders, dtype):
+    """A request's logits are the same alone and in a batch, up to rounding of the same kernels."""
+    from stratakv_b200 import StepEntry
+    name = "B"
+    engine = engine_for(folders[name], dtype)
+    vocab = TINY[name]["vocab_size"]
+    tokens = random_tokens(vocab, 23, seed=5)
+    slot = engine.open_sequence()
+    alone = engine.step([StepEntry(slot, tokens, [22])]).clone()
+    engine.close_sequence(slot)
+    others = [random_tokens(vocab, n, seed=50 + n) for n in (3, 61, 8)]
+    slots = [engine.open_sequence() for _ in range(4)]
+    entries = [StepEntry(slots[0], others[0], []), StepEntry(slots[1], others[1], [0]),
+               StepEntry(slots[2], tokens, [22]), StepEntry(slots[3], others[2], [])]
+    together = engine.step(entries)[1:2].clone()
+    rtol, atol = (1e-5, 1e-6) if dtype == "float32" else (2e-2, 2e-2)
+    torch.testing.assert_close(together, alone, rtol=rtol, atol=atol)
+    for s in slots:
+        engine.close_sequence(s)

@@ -1,0 +1,258 @@
+"""Each kernel alone against a plain float32 computation of the same op, at sizes
+other than the engine's (odd counts, sizes that are no power of two)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def lib(dtype, head_dim=64):
+    from stratakv_b200.ops import kernels_for
+    return kernels_for(dtype, head_dim, verbose=False)
+
+
+def close(got, ref, dtype, scale=1.0):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    if dtype == torch.float32:
+        torch.testing.assert_close(got, ref, rtol=2e-5, atol=2e-6 * scale)
+    else:
+        torch.testing.assert_close(got, ref, rtol=1.6e-2, atol=1e-2 * scale)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,hidden,n", [(331, 80, 7), (1000, 2048, 33)])
+def test_embed(dtype, vocab, hidden, n):
+    k = lib(dtype)
+    table = torch.randn(vocab, hidden, device="cuda").to(dtype)
+    ids = torch.randint(0, vocab, (n,), device="cuda", dtype=torch.int32)
+    out = torch.full((n, hidden), float("nan"), device="cuda")
+    k.embed(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,eps", [(5, 80, 1e-5), (3, 2048, 1e-6), (9, 1000, 3e-3)])
+def test_rmsnorm(dtype, rows, hidden, eps):
+    k = lib(dtype)
+    x = torch.randn(rows, hidden, device="cuda") * 3.0
+    gamma = 1.0 + 0.1 * torch.randn(hidden, device="cuda")
+    out = torch.full((rows, hidden), float("nan"), device="cuda").to(dtype)
+    k.rmsnorm(x, gamma, eps, out)
+    xd = x.double()
+    ref = (xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + eps) * gamma.double()).float()
+    close(out, ref, dtype, scale=3.0)
+    # with a row selection
+    rows_index = torch.tensor([rows - 1, 0], device="cuda", dtype=torch.int32)
+    picked = torch.full((2, hidden), float("nan"), device="cuda").to(dtype)
+    k.rmsnorm(x, gamma, eps, picked, rows_index)
+    close(picked, ref[rows_index.long()], dtype, scale=3.0)
+
+
+def pack_gate_up(w):
+    from stratakv_b200.parts.ffn import pack_gate_up as pack
+    half = w.shape[0] // 2
+    return pack(w[:half].contiguous(), w[half:].contiguous())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (3, 331, 80), (8, 256, 2048), (9, 100, 264), (17, 96, 96),
+                                   (33, 80, 176), (64, 512, 512), (70, 130, 520), (200, 64, 72)])
+def test_linear_store_and_add(dtype, M, N, K):
+    from stratakv_b200 import ops
+    k = lib(dtype)
+    a = torch.randn(M, K, device="cuda").to(dtype)
+    w = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(dtype)
+    ref = a.double() @ w.double().T
+    bound = (a.double().abs() @ w.double().abs().T)
+    out = torch.full((M, N), float("nan"), device="cuda")
+    k.linear(a, w, out, ops.MODE_STORE_F32)
+    # accumulation in float: error grows with the sum of |a||w| (tests/gemv_smoke.cu:259-272)
+    assert ((out.double() - ref).abs() <= 2e-6 * (1 + bound)).all()
+    out_t = torch.full((M, N), float("nan"), device="cuda").to(dtype)
+    k.linear(a, w, out_t, ops.MODE_STORE)
+    close(out_t, ref, dtype)
+    base = torch.randn(M, N, device="cuda")
+    acc = base.clone()
+    k.linear(a, w, acc, ops.MODE_ADD_F32)
+    k.linear(a, w, acc, ops.MODE_ADD_F32)       # a second call must add again, not overwrite
+    assert ((acc.double() - (base.double() + 2 * ref)).abs() <= 4e-6 * (1 + bound) + 1e-6 * base.abs()).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,F,K", [(1, 176, 64), (5, 104, 80), (8, 5632, 2048), (40, 256, 96), (130, 24, 72)])
+def test_linear_gated(dtype, M, F, K):
+    from stratakv_b200 import ops
+    k = lib(dtype)
+    a = torch.randn(M, K, device="cuda").to(dtype)
+    w = (torch.randn(2 * F, K, device="cuda") / math.sqrt(K)).to(dtype)      # gate rows, then up rows
+    out = torch.full((M, F), float("nan"), device="cuda").to(dtype)
+    k.linear(a, pack_gate_up(w), out, ops.MODE_GATED, "silu")
+    gate = a.double() @ w[:F].double().T
+    up = a.double() @ w[F:].double().T
+    close(out, gate * torch.sigmoid(gate) * up, dtype)
+
+
+def test_linear_refuses_bad_sizes():
+    from stratakv_b200 import ops
+    from stratakv_b200.ops import KernelError
+    k = lib(torch.bfloat16)
+    a = torch.zeros(2, 12, device="cuda", dtype=torch.bfloat16)
+    w = torch.zeros(16, 12, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        k.linear(a, w, torch.zeros(2, 16, device="cuda"), ops.MODE_STORE_F32)
+    with pytest.raises(KernelError, match="CUDA tensor"):
+        k.linear(a.cpu(), w, torch.zeros(2, 16, device="cuda"), ops.MODE_STORE_F32)
+
+
+def paged_setup(dtype, lengths, new, heads, kv_heads, head_dim, block_size, seed):
+    """Random q/k/v for sequences with ``lengths[i]`` cached tokens after a step that
+    adds ``new[i]``; blocks are handed out in a scrambled order."""
+    g = torch.Generator().manual_seed(seed)
+    n_seq = len(lengths)
+    width = max(-(-l // block_size) for l in lengths)
+    n_blocks = n_seq * width + 3
+    order = torch.randperm(n_blocks, generator=g).tolist()
+    table = torch.zeros(n_seq, width, dtype=torch.int32)
+    for s in range(n_seq):
+        for b in range(-(-lengths[s] // block_size)):
+            table[s, b] = order.pop()
+    k_cache = torch.zeros(n_blocks, kv_heads, block_size, head_dim)
+    v_cache = torch.zeros_like(k_cache)
+    keys = [torch.randn(l, kv_heads, head_dim, generator=g) for l in lengths]
+    values = [torch.randn(l, kv_heads, head_dim, generator=g) for l in lengths]
+    for s in range(n_seq):
+        for j in range(lengths[s]):
+            k_cache[table[s, j // block_size], :, j % block_size] = keys[s][j]
+            v_cache[table[s, j // block_size], :, j % block_size] = values[s][j]
+    positions, token_seq = [], []
+    for s in range(n_seq):
+        positions += list(range(lengths[s] - new[s], lengths[s]))
+        token_seq += [s] * new[s]
+    q = torch.randn(len(positions), heads, head_dim, generator=g)
+    to = lambda t: t.to("cuda").to(dtype)
+    return dict(q=to(q), k_cache=to(k_cache), v_cache=to(v_cache), table=table.cuda(),
+                positions=torch.tensor(positions, dtype=torch.int32).cuda(),
+                token_seq=torch.tensor(token_seq, dtype=torch.int32).cuda(),
+                keys=keys, values=values)
+
+
+def attention_reference(setup, dtype, heads, kv_heads, scale, window=0):
+    q = setup["q"].float().cpu()
+    out = torch.zeros_like(q)
+    group = heads // kv_heads
+    for t in range(q.shape[0]):
+        s, pos = int(setup["token_seq"][t]), int(setup["positions"][t])
+        lo = max(0, pos - window + 1) if window else 0
+        keys = setup["keys"][s][lo:pos + 1].to(dtype).double()
+        values = setup["values"][s][lo:pos + 1].to(dtype).double()
+        for h in range(heads):
+            weights = torch.softmax((keys[:, h // group] @ q[t, h].double()) * scale, dim=0)
+            out[t, h] = (weights @ values[:, h // group]).float()
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size,lengths,new,window", [
+    (4, 2, 16, 16, [5, 40, 17], [5, 40, 17], 0),          # prompts from the start
+    (6, 3, 48, 16, [33, 1, 100], [1, 1, 1], 0),           # one new token each
+    (8, 1, 64, 64, [70, 129], [6, 65], 0),                # continuing a prompt
+    (5, 5, 128, 32, [300], [1], 0),
+    (4, 2, 32, 16, [90, 45], [90, 1], 20),                # a window of 20 keys
+])
+def test_attention(dtype, heads, kv_heads, head_dim, block_size, lengths, new, window):
+    k = lib(dtype, head_dim)
+    setup = paged_setup(dtype, lengths, new, heads, kv_heads, head_dim, block_size, seed=head_dim + heads)
+    n = setup["q"].shape[0]
+    out = torch.full((n, heads * head_dim), float("nan"), device="cuda").to(dtype)
+    scale = 0.37 / math.sqrt(head_dim)
+    k.attention(setup["q"].view(n, -1), setup["k_cache"], setup["v_cache"], setup["table"], setup["positions"],
+                setup["token_seq"], out, heads, kv_heads, head_dim, block_size, scale, window)
+    ref = attention_reference(setup, dtype, heads, kv_heads, scale, window).view(n, -1)
+    close(out, ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dtype):
+    """One key among hundreds is made to dominate: the output must be that key's value."""
+    heads, kv_heads, head_dim, block_size = 4, 2, 32, 16
+    k = lib(dtype, head_dim)
+    for far in (0, 15, 16, 257, 511):
+        setup = paged_setup(dtype, [512], [1], heads, kv_heads, head_dim, block_size, seed=far)
+        q = setup["q"].float()
+        key = 8.0 * q[0, 0] / q[0, 0].norm()                   # aligned with head 0's query
+        block = int(setup["table"][0, far // block_size])
+        setup["k_cache"][block, 0, far % block_size] = key.to(dtype)
+        setup["keys"][0][far, 0] = key.cpu()
+        out = torch.zeros(1, heads * head_dim, device="cuda").to(dtype)
+        k.attention(setup["q"].view(1, -1), setup["k_cache"], setup["v_cache"], setup["table"],
+                    setup["positions"], setup["token_seq"], out, heads, kv_heads, head_dim, block_size,
+                    4.0, 0)
+        ref = attention_reference(setup, dtype, heads, kv_heads, 4.0).view(1, -1)
+        close(out, ref, dtype)
+        want = setup["values"][0][far, 0].to(dtype).float()
+        torch.testing.assert_close(out[0, :head_dim].float().cpu(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size", [(4, 2, 16, 16), (3, 3, 80, 64), (8, 2, 128, 32)])
+def test_rope_kv_write(dtype, heads, kv_heads, head_dim, block_size):
+    from stratakv_b200.parts.position import rope_table
+    k = lib(dtype, head_dim)
+    lengths, new = [37, 5, 130], [37, 1, 66]
+    setup = paged_setup(dtype, lengths, new, heads, kv_heads, head_dim, block_size, seed=3)
+    n = setup["q"].shape[0]
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(n, (heads + 2 * kv_heads) * head_dim, generator=g).cuda()
+    theta = 25000.0
+    table = torch.from_numpy(rope_table(head_dim, theta, 256)).cuda()
+    k_cache = torch.full_like(setup["k_cache"], 7.0)
+    v_cache = torch.full_like(setup["v_cache"], 7.0)
+    q_out = torch.full((n, heads * head_dim), float("nan"), device="cuda").to(dtype)
+    k.rope_kv_write(qkv, table, setup["positions"], setup["token_seq"], setup["table"], q_out, k_cache, v_cache,
+                    heads, kv_heads, head_dim, block_size, True)
+    # plain: angles in double, rotation in float
+    half = head_dim // 2
+    pos = setup["positions"].cpu().double()
+    inv = torch.tensor([theta ** (-2.0 * i / head_dim) for i in range(half)], dtype=torch.float64).float().double()
+    angle = pos[:, None] * inv[None, :]
+    cos, sin = torch.cos(angle).float(), torch.sin(angle).float()
+    src = qkv.cpu()
+    q = src[:, :heads * head_dim].view(n, heads, head_dim)
+    kk = src[:, heads * head_dim:(heads + kv_heads) * head_dim].view(n, kv_heads, head_dim)
+    vv = src[:, (heads + kv_heads) * head_dim:].view(n, kv_heads, head_dim)
+    rot = lambda x: torch.cat([x[..., :half] * cos[:, None] - x[..., half:] * sin[:, None],
+                               x[..., :half] * sin[:, None] + x[..., half:] * cos[:, None]], -1)
+    exact = dtype == torch.float32
+    got_q = q_out.float().cpu().view(n, heads, head_dim)
+    torch.testing.assert_close(got_q, rot(q).to(dtype).float(), rtol=0 if exact else 8e-3, atol=1e-6 if exact else 1e-2)
+    kc, vc = k_cache.float().cpu(), v_cache.float().cpu()
+    touched = torch.zeros(kc.shape[0], block_size, dtype=torch.bool)
+    for t in range(n):
+        s, p = int(setup["token_seq"][t]), int(setup["positions"][t])
+        block = int(setup["table"][s, p // block_size])
+        touched[block, p % block_size] = True
+        torch.testing.assert_close(kc[block, :, p % block_size], rot(kk)[t].to(dtype).float(),
+                                   rtol=0 if exact else 8e-3, atol=1e-6 if exact else 1e-2)
+        assert torch.equal(vc[block, :, p % block_size], vv[t].to(dtype).float())
+    # rows no token of this step owns keep their old contents
+    assert (kc.permute(0, 2, 1, 3)[~touched] == 7.0).all() and (vc.permute(0, 2, 1, 3)[~touched] == 7.0).all()
+
+
+def test_argmax_lowest_index_among_equals():
+    k = lib(torch.float32)
+    logits = torch.randn(5, 1000, device="cuda")
+    logits[0, 700] = logits[0, 20] = 50.0
+    logits[3, 999] = 60.0
+    out = torch.zeros(5, dtype=torch.int32, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    k.argmax(logits, out, flag)
+    ref = torch.argmax(logits, dim=-1).cpu()
+    ref[0] = 20
+    assert out.cpu().tolist() == ref.tolist() and int(flag) == 0
+    logits[2, 5] = float("nan")
+    k.argmax(logits, out, flag)
+    assert int(flag) & 2
