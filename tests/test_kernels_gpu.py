@@ -74,7 +74,8 @@ def test_linear_store_and_add(dtype, M, N, K):
     assert ((out.double() - ref).abs() <= 2e-6 * (1 + bound)).all()
     out_t = torch.full((M, N), float("nan"), device="cuda").to(dtype)
     k.linear(a, w, out_t, ops.MODE_STORE)
-    close(out_t, ref, dtype)
+    rounding = 0.0 if dtype == torch.float32 else 2.0 ** -8       # one rounding of the result to bfloat16
+    assert ((out_t.double() - ref).abs() <= 2e-6 * (1 + bound) + rounding * ref.abs()).all()
     base = torch.randn(M, N, device="cuda")
     acc = base.clone()
     k.linear(a, w, acc, ops.MODE_ADD_F32)
@@ -93,7 +94,16 @@ def test_linear_gated(dtype, M, F, K):
     k.linear(a, pack_gate_up(w), out, ops.MODE_GATED, "silu")
     gate = a.double() @ w[:F].double().T
     up = a.double() @ w[F:].double().T
-    close(out, gate * torch.sigmoid(gate) * up, dtype)
+    ref = gate * torch.sigmoid(gate) * up
+    if dtype == torch.float32:
+        # float accumulation errs by at most ~2e-6 (1 + sum |a||w|) in gate and in up
+        # (tests/gemv_smoke.cu:259-272); silu has slope <= 1.1
+        err_gate = 2e-6 * (1 + a.double().abs() @ w[:F].double().abs().T)
+        err_up = 2e-6 * (1 + a.double().abs() @ w[F:].double().abs().T)
+        allowed = 1.1 * err_gate * up.abs() + (gate * torch.sigmoid(gate)).abs() * err_up + 1e-6 * ref.abs() + 1e-9
+        assert ((out.double() - ref).abs() <= allowed).all()
+    else:
+        close(out, ref, dtype)
 
 
 def test_linear_refuses_bad_sizes():
