@@ -179,6 +179,34 @@ class Engine:
             self.cache.advance(e.slot, self.cache.length(e.slot) + len(e.tokens))
         return logits
 
+    def generate(self, prompts, max_new_tokens, params=None, stop_ids=None, ignore_eos: bool = False,
+                 streams=None):
+        """Generate for a list of prompts (lists of token ids).  Returns a
+        ``GenerationOutput`` whose ``sequences[i]`` is prompt ``i`` followed by its
+        new tokens.  ``stop_ids`` defaults to the model's end-of-sequence ids;
+        ``ignore_eos`` generates to the budget regardless."""
+        from ..sampling import Sampler, SamplingParams
+        from .generate import generate as run
+        params = params or SamplingParams()
+        sampler = Sampler(self.rt.kernels(), params, self.model.flags)
+        if ignore_eos:
+            stop_ids = ()
+        elif stop_ids is None:
+            stop_ids = self.spec.stop_token_ids
+
+        def choose(logits, row_streams, counters):
+            if params.greedy:
+                tokens = sampler.sample(logits, None, None)
+            else:
+                meta = torch.tensor([row_streams, counters], dtype=torch.int32).to(self.device)
+                tokens = sampler.sample(logits, meta[0], meta[1])
+            return tokens.tolist()
+
+        sync = torch.cuda.synchronize if self.device.type == "cuda" else (lambda: None)
+        output = run(self, choose, prompts, max_new_tokens, stop_ids, streams, sync=sync)
+        self.check_flags()
+        return output
+
     def check_flags(self) -> None:
         """Raise if a kernel flagged bad input since the last check (reads one word from the device)."""
         flags = int(self.model.flags.item())

@@ -149,6 +149,18 @@ class Kernels:
         rows, vocab = logits.shape
         self._check(self.lib.skv_argmax(_ptr(logits), _ptr(out), rows, vocab, _ptr(flag), _stream()), "argmax")
 
+    def sample(self, logits, out, temperature: float, top_k: int, top_p: float, seed: int, streams, counters,
+               flag=None):
+        """Temperature / top-k / top-p draw per row; row r uses random number (seed, streams[r], counters[r])."""
+        self._want(logits, torch.float32, "logits"); self._want(out, torch.int32, "out")
+        self._want(streams, torch.int32, "streams"); self._want(counters, torch.int32, "counters")
+        rows, vocab = logits.shape
+        if streams.numel() != rows or counters.numel() != rows or out.numel() != rows:
+            raise KernelError("sample: one stream, counter and output per row is needed")
+        self._check(self.lib.skv_sample(_ptr(logits), _ptr(out), rows, vocab, ctypes.c_float(temperature),
+                                        int(top_k), ctypes.c_float(top_p), ctypes.c_ulonglong(seed),
+                                        _ptr(streams), _ptr(counters), _ptr(flag), _stream()), "sample")
+
 
 _LOADED: Dict[Tuple[torch.dtype, int], Kernels] = {}
 

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import json
 import mmap
+import os
 import struct
 from dataclasses import dataclass
 from pathlib import Path
@@ -191,9 +192,14 @@ def write_safetensors(path, tensors: Mapping[str, torch.Tensor], metadata=None) 
         cursor += nbytes
     text = json.dumps(header, separators=(",", ":")).encode("utf-8")
     text += b" " * ((8 - len(text) % 8) % 8)  # keeps the payload 8-byte aligned
-    with open(path, "wb") as out:
+    # Written beside the target and renamed over it: a file that is mapped
+    # somewhere (even by the tensors being written) is never truncated.
+    path = Path(path)
+    staged = path.with_name(path.name + f".tmp{os.getpid()}")
+    with open(staged, "wb") as out:
         out.write(struct.pack("<Q", len(text)))
         out.write(text)
         for name in order:
             tensor = tensors[name].detach().cpu().contiguous()
             out.write(tensor.reshape(-1).view(torch.uint8).numpy().tobytes())
+    os.replace(staged, path)
