@@ -1,0 +1,293 @@
+"""Benchmark: decode tokens a second and prefill tokens a second on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+
+The default run has the layer sizes of the TinyLlama-1.1B shape (22 layers,
+hidden 2048, 32 heads, 4 KV heads, head size 64, feed-forward 5632, vocabulary
+32000) with random bfloat16 weights, a batch of 8 and a context that ends at
+2,048 tokens.  A "step" is one decode step of the whole batch.  It prints one
+JSON line:
+
+  value        decoded tokens a second, timed on the device around K steps
+  e2e          the same through the Python entry point (``Engine.generate``):
+               token ids go in from pinned host memory and come back to the
+               host every step
+  prefill      one 2,048-token prompt: tokens a second, ms, and the fraction
+               of the bf16 tensor peak its FLOPs reach
+  roofline     the decode step against HBM: bytes it must read (every weight
+               once, plus the cache of the live requests) over its time
+  points       decode tokens a second at batch 1 and 64
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# The TinyLlama-1.1B shape (sizes only; weights are random).
+TINYLLAMA = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermediate_size=5632,
+                 num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4, head_dim=64,
+                 vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=2048,
+                 tie_word_embeddings=False, hidden_act="silu")
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "source": "measured"}
+        except (ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index=0):
+        self.samples, self.process, self.thread = [], None, None
+        self.device_index = device_index
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.process.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, reasons, max_clock = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for parts in self.samples:
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[2:]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def make_engine(layers: int, max_tokens: int, max_batch: int):
+    import torch
+    from stratakv_b200 import Engine, EngineConfig, LlamaConfig
+    raw = dict(TINYLLAMA, num_hidden_layers=layers)
+    config = LlamaConfig.from_dict(raw)
+    engine_config = EngineConfig(max_tokens=max_tokens, dtype="bfloat16", max_batch=max_batch)
+    from stratakv_b200.config.registry import resolve_architecture
+    from stratakv_b200.engine.model import expected_tensors
+    from stratakv_b200.weights import random_tensors
+    spec = resolve_architecture(config.architecture).build_spec(config)
+    tensors = random_tensors(expected_tensors(spec), seed=0, dtype=torch.bfloat16, device="cuda")
+    engine = Engine(spec, tensors, engine_config, verbose=False)
+    engine.model_config = config
+    return engine, config
+
+
+def random_ids(count, vocab, seed):
+    import torch
+    generator = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (count,), generator=generator).tolist()
+
+
+def fill_context(engine, batch, context, vocab):
+    """Open ``batch`` sequences and prefill each with ``context`` random tokens."""
+    from stratakv_b200 import StepEntry
+    slots = []
+    for index in range(batch):
+        slot = engine.open_sequence()
+        engine.step([StepEntry(slot, random_ids(context, vocab, 1000 + index), [])])
+        slots.append(slot)
+    return slots
+
+
+def time_decode(engine, batch, start_context, steps, warmup, vocab):
+    """Device time of ``steps`` decode steps of ``batch`` sequences (ms per step), sampling included."""
+    import torch
+    from stratakv_b200.sampling import Sampler, SamplingParams
+    from stratakv_b200 import StepEntry
+    slots = fill_context(engine, batch, start_context, vocab)
+    sampler = Sampler(engine.rt.kernels(), SamplingParams(), engine.model.flags)
+    chosen = torch.empty(batch, dtype=torch.int32, device=engine.device)
+    entries = [StepEntry(slot, [token], [0]) for slot, token in zip(slots, random_ids(batch, vocab, 7))]
+
+    def one_step():
+        sampler.sample(engine.step(entries), None, None, chosen)
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    launches_before = engine.launch_count()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        one_step()
+    end.record()
+    torch.cuda.synchronize()
+    launches = engine.launch_count() - launches_before
+    final_context = engine.cache.length(slots[0])
+    for slot in slots:
+        engine.close_sequence(slot)
+    return begin.elapsed_time(end) / steps, launches, final_context
+
+
+def time_e2e(engine, batch, start_context, steps, vocab):
+    """Tokens a second through ``Engine.generate``: host token ids in, host token ids out, every step."""
+    prompts = [random_ids(start_context, vocab, 2000 + i) for i in range(batch)]
+    engine.generate(prompts[:1], 4, ignore_eos=True)                          # warm-up of both step kinds
+    output = engine.generate(prompts, steps + 1, ignore_eos=True)
+    timings = output.timings
+    return timings, engine.last_step_io_bytes()
+
+
+def time_prefill(engine, tokens, vocab, repeats=3):
+    import torch
+    from stratakv_b200 import StepEntry
+    times = []
+    for repeat in range(repeats + 1):
+        slot = engine.open_sequence()
+        ids = random_ids(tokens, vocab, 3000 + repeat)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        engine.step([StepEntry(slot, ids, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        engine.close_sequence(slot)
+        if repeat:                                    # the first run is the warm-up
+            times.append(begin.elapsed_time(end))
+    return statistics.median(times)
+
+
+def prefill_flops(config, tokens):
+    per_token = 2 * (config.hidden_size * (config.q_dim + 2 * config.kv_dim) + config.q_dim * config.hidden_size
+                     + 3 * config.hidden_size * config.intermediate_size)
+    linear = config.num_hidden_layers * per_token * tokens + 2 * config.hidden_size * config.vocab_size
+    attention = config.num_hidden_layers * 4 * config.num_attention_heads * config.head_dim * tokens * (tokens + 1) // 2
+    return linear + attention
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "pip cannot install the reference: it is a CMake C++/CUDA project with neither setup.py "
+                      "nor pyproject.toml, and its kernels target sm_61"}))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=TINYLLAMA["num_hidden_layers"])
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+    steps = max(args.steps, 1)
+
+    import torch
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    vocab = TINYLLAMA["vocab_size"]
+    start_context = CONTEXT - steps - warmup                 # the timed steps end at the named context
+    if start_context < 1:
+        print("bench.py: --steps plus --warmup must stay below the context of 2048")
+        return 1
+    biggest = 64 if not args.skip_points else args.batch
+    max_tokens = max(biggest * (CONTEXT + 64), PREFILL_TOKENS + 64)
+    engine, config = make_engine(args.layers, max_tokens, max(biggest, args.batch))
+    peak = peaks()
+
+    sampler = ClockSampler()
+    sampler.start()
+    ms_per_step, launches, final_context = time_decode(engine, args.batch, start_context, steps, warmup, vocab)
+    clocks = sampler.stop()
+    value = args.batch * 1000.0 / ms_per_step
+
+    timings, io_bytes = time_e2e(engine, args.batch, start_context, steps, vocab)
+    e2e = {"value": timings.decode_tps, "unit": "tokens/s", "h2d_bytes_per_step": io_bytes[0],
+           "d2h_bytes_per_step": io_bytes[1], "prefill_ms": timings.prefill_ms}
+
+    weight_bytes = engine.model.weight_bytes()
+    mean_context = final_context - steps / 2
+    kv_bytes = args.batch * mean_context * engine.cache.bytes_per_token()
+    achieved = (weight_bytes + kv_bytes) / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peak["hbm_gbs"], "of": peak["source"], "weight_bytes": weight_bytes,
+                "kv_bytes": int(kv_bytes)}
+
+    result = {
+        "metric": "decode tokens/s (TinyLlama-1.1B shape, bf16, batch 8, context 2048)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": value / 33.8,
+        "dtype": "bf16", "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
+        "config": {"model": "TinyLlama-1.1B shape", "layers": args.layers, "layers_of_model": TINYLLAMA["num_hidden_layers"],
+                   "hidden": config.hidden_size, "heads": config.num_attention_heads,
+                   "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
+                   "ffn": config.intermediate_size, "vocab": config.vocab_size, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "context_at_end": final_context, "parallelism": "single GPU",
+                   "cache_block": engine.cache.block_size, "l2": "inputs larger than L2 (weights 2.2 GB per step)"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "impl": "ours",
+    }
+    if not args.skip_points:
+        prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab)
+        flops = prefill_flops(config, PREFILL_TOKENS)
+        result["prefill"] = {"value": PREFILL_TOKENS * 1000.0 / prefill_ms, "tokens": PREFILL_TOKENS,
+                             "ms": prefill_ms, "frac": flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12),
+                             "of": peak["source"]}
+        points = {}
+        for batch in (1, 64):
+            ms, _, _ = time_decode(engine, batch, start_context, steps, warmup, vocab)
+            points[f"decode_b{batch}"] = batch * 1000.0 / ms
+        result["points"] = points
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -40,6 +40,7 @@ class CacheGroup:
 
 @dataclass
 class SequenceRecord:
+    serial: int = 0                       # distinguishes successive users of one slot
     length: int = 0
     blocks: Dict[int, List[int]] = field(default_factory=dict)    # group -> block ids by logical block
     dropped: Dict[int, int] = field(default_factory=dict)          # group -> leading logical blocks freed
@@ -73,7 +74,8 @@ class KVCache:
             self.entry_group.append((group.index, len(group.entries)))
             group.entries.append(entry)
         for group in self.groups:
-            shape = (len(group.entries), num_blocks, group.request.num_kv_heads, block_size,
+            # one block more than the allocator hands out: padding rows of a step write there
+            shape = (len(group.entries), num_blocks + 1, group.request.num_kv_heads, block_size,
                      group.request.head_dim)
             group.keys = torch.zeros(shape, dtype=dtype, device=self.device)
             group.values = torch.zeros(shape, dtype=dtype, device=self.device)
@@ -82,6 +84,8 @@ class KVCache:
         self._state = {entry: torch.zeros((max_slots, r.state_bytes), dtype=torch.uint8, device=self.device)
                        for entry, r in enumerate(requests) if r.state_bytes > 0}
         self.sequences: Dict[int, SequenceRecord] = {}
+        self.trash_block = num_blocks         # owned by no sequence
+        self._serial = 0
 
     # ---- storage views ---------------------------------------------------
     def entry_kv(self, entry: int):
@@ -106,8 +110,9 @@ class KVCache:
     def acquire(self) -> int:
         """A free slot for a new sequence; its state rows are zeroed."""
         (slot,) = self.slots.take(1)
+        self._serial += 1
         self.sequences[slot] = SequenceRecord(
-            blocks={g.index: [] for g in self.groups}, dropped={g.index: 0 for g in self.groups})
+            serial=self._serial, blocks={g.index: [] for g in self.groups}, dropped={g.index: 0 for g in self.groups})
         for state in self._state.values():
             state[slot].zero_()
         return slot

@@ -58,6 +58,12 @@ class Engine:
                              config.dtype, self.device)
         self._pinned: Optional[torch.Tensor] = None
         self._meta: Optional[torch.Tensor] = None
+        self._copied = None
+        self._graphs = {}
+        self._use_graphs = (config.use_cuda_graphs and self.device.type == "cuda" and self.model.graph_safe())
+        self.graph_launches = 0
+        self._launch_base = _ops.Kernels.launches
+        self._io_bytes = (0, 0)
 
     # ---- construction ----------------------------------------------------------
     @classmethod
@@ -153,8 +159,13 @@ class Engine:
             for row in rows:
                 flat.extend(row)
         pinned, meta = self._metadata(len(flat))
+        if self._copied is not None:
+            self._copied.synchronize()          # the last step's copy must have left the pinned array
         pinned[:len(flat)] = torch.tensor(flat, dtype=torch.int32)
         meta[:len(flat)].copy_(pinned[:len(flat)], non_blocking=True)
+        if self.device.type == "cuda":
+            self._copied = self._copied or torch.cuda.Event()
+            self._copied.record()
 
         def view(key):
             start, count = offsets[key]
@@ -173,11 +184,74 @@ class Engine:
         """Run one step.  Returns float32 logits ``[wanted, vocab]`` on the device,
         in the order of the entries and of their ``want`` (``None`` when nothing
         is wanted).  The tensor is scratch memory: use or copy it before the next step."""
+        if self._use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
+            return self._decode_step(entries)
         step, want_rows, n_want = self.prepare(entries)
         logits = self.model.forward(step, want_rows, n_want)
         for e in entries:
             self.cache.advance(e.slot, self.cache.length(e.slot) + len(e.tokens))
         return logits
+
+    def _decode_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """One token per sequence: the step runs as a CUDA graph of its batch-size bucket."""
+        from .decode_graph import DecodeGraph, bucket_for
+        vocab = self.spec.vocab_size
+        slots = [e.slot for e in entries]
+        if len(set(slots)) != len(slots):
+            raise StepError("a sequence appears twice in one step")
+        if len(entries) > self.config.slots:
+            raise StepError(f"{len(entries)} sequences in one step; the engine holds {self.config.slots}")
+        tokens, ctx_before, wanted, rows = [], [], {}, []
+        for index, e in enumerate(entries):
+            if e.slot not in self.cache.sequences:
+                raise StepError(f"slot {e.slot} is not open")
+            token = int(e.tokens[0])
+            if not (0 <= token < vocab):
+                raise StepError(f"slot {e.slot}: token id {token} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if int(w) != 0:
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside this step's 1 tokens")
+                rows.append(index)
+            before = self.cache.length(e.slot)
+            tokens.append(token)
+            ctx_before.append(before)
+            wanted[e.slot] = before + 1
+        self.cache.reserve(wanted)
+        need = -(-max(wanted.values()) // self.cache.block_size)
+        bucket = bucket_for(len(entries))
+        graph = self._graphs.get(bucket)
+        if graph is None or graph.width < need:
+            width = 4
+            while width < need:
+                width *= 2
+            graph = DecodeGraph(self, bucket, width)
+            self._graphs[bucket] = graph
+        graph.fill(slots, tokens, ctx_before)
+        logits = graph.run()
+        self._io_bytes = (graph.host.numel() * 4, self._io_bytes[1])
+        for slot, length in wanted.items():
+            self.cache.advance(slot, length)
+        if not rows:
+            return None
+        if len(rows) == len(entries):
+            return logits[:len(entries)]
+        return logits[torch.tensor(rows, device=self.device)]
+
+    # ---- accounting ------------------------------------------------------------------
+    def kernel_launches(self) -> int:
+        return _ops.Kernels.launches - self._launch_base
+
+    def discount_launches(self, count: int) -> None:
+        """Calls made while a graph was being captured were recorded, not run."""
+        self._launch_base += count
+
+    def launch_count(self) -> int:
+        """Kernels of this library launched so far, graph replays included."""
+        return self.kernel_launches() + self.graph_launches
+
+    def last_step_io_bytes(self):
+        """(host-to-device, device-to-host) bytes of the most recent decode step."""
+        return self._io_bytes
 
     def generate(self, prompts, max_new_tokens, params=None, stop_ids=None, ignore_eos: bool = False,
                  streams=None):
@@ -200,6 +274,7 @@ class Engine:
             else:
                 meta = torch.tensor([row_streams, counters], dtype=torch.int32).to(self.device)
                 tokens = sampler.sample(logits, meta[0], meta[1])
+            self._io_bytes = (self._io_bytes[0], tokens.numel() * 4)
             return tokens.tolist()
 
         sync = torch.cuda.synchronize if self.device.type == "cuda" else (lambda: None)

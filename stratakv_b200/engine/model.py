@@ -92,6 +92,16 @@ class Model:
                 part.bind(tensors)
         self.final_norm.bind(tensors)
 
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for layer in self.layers for part in layer.parts()) and self.final_norm.graph_safe
+
+    def prepare_positions(self, max_positions: int) -> None:
+        """Let position encodings build their tables up to ``max_positions`` (before a graph capture)."""
+        for layer in self.layers:
+            position = getattr(layer.mixer, "position", None)
+            if position is not None:
+                position.ensure(max_positions)
+
     def weight_bytes(self) -> int:
         """Bytes of weights one decode step reads (each matrix once; one embedding row per token is left out)."""
         seen, total = set(), 0

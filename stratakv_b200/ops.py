@@ -33,6 +33,8 @@ def _stream():
 class Kernels:
     """The kernels of one (compute dtype, head size) library."""
 
+    launches = 0          # kernel launches issued through any library of this process
+
     def __init__(self, dtype: torch.dtype, head_dim: int, verbose: bool = True):
         if dtype not in _DTYPE_NAMES:
             raise KernelError(f"no kernels for dtype {dtype}")
@@ -52,6 +54,7 @@ class Kernels:
 
     # ---- helpers -----------------------------------------------------------
     def _check(self, code: int, name: str) -> None:
+        Kernels.launches += 1
         if code != 0:
             raise KernelError(f"{name}: {self.lib.skv_last_error().decode()}")
 
@@ -136,6 +139,27 @@ class Kernels:
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(positions),
             _ptr(token_seq), _ptr(out), n, num_heads, num_kv_heads, head_dim, block_size,
             ctypes.c_float(scale), window, _stream()), "attention")
+
+    def attention_decode(self, q, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
+                         num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
+                         splits: int = 1, scratch_o=None, scratch_ml=None):
+        """One new token per sequence (bfloat16 build): ``ctx_after[s]`` keys are cached for sequence
+        ``s``, the newest being the query's own.  ``splits`` > 1 cuts each context across blocks and
+        needs float scratch: ``scratch_o`` [seqs*heads*splits*head_dim], ``scratch_ml`` [seqs*heads*splits*2]."""
+        self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
+        self._want(block_table, torch.int32, "block_table"); self._want(ctx_after, torch.int32, "ctx_after")
+        n = q.shape[0]
+        if ctx_after.numel() != n or block_table.shape[0] != n:
+            raise KernelError("attention_decode: one length and one table row per sequence is needed")
+        if splits > 1:
+            self._want(scratch_o, torch.float32, "scratch_o"); self._want(scratch_ml, torch.float32, "scratch_ml")
+            if scratch_o.numel() < n * num_heads * splits * head_dim or scratch_ml.numel() < n * num_heads * splits * 2:
+                raise KernelError("attention_decode: scratch is too small for this many splits")
+        self._check(self.lib.skv_attention_decode(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(ctx_after),
+            _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), n, num_heads, num_kv_heads, head_dim, block_size,
+            ctypes.c_float(scale), window, splits, _stream()), "attention_decode")
 
     def add_inplace(self, out, other):
         self._want(out, torch.float32, "out"); self._want(other, torch.float32, "other")

@@ -17,7 +17,18 @@ from .base import CacheRequest, Mixer, TensorRequest
 from .registry import part_class, register_mixer
 
 
+def decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148) -> int:
+    """Into how many pieces a decode step cuts each context: enough blocks to fill the
+    GPU twice over, at least 128 keys (one group of 16 per warp) a piece.  It depends on
+    the step's sizes only, never on which sequences are live."""
+    by_length = max(1, max_ctx // 128)
+    by_count = -(-2 * sms // max(1, n_seqs * blocks_per_seq))
+    return max(1, min(by_length, by_count, 64))
+
+
 class PagedAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         if spec.num_heads % spec.num_kv_heads != 0:
@@ -63,8 +74,17 @@ class PagedAttention(Mixer):
         self.position.rotate_and_store(step, qkv, q, k_cache, v_cache, table, s.num_heads, s.num_kv_heads,
                                        s.head_dim, step.cache.block_size, writes_cache)
         ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
-        ops.attention(q, k_cache, v_cache, table, step.positions, step.token_seq, ctx, s.num_heads,
-                      s.num_kv_heads, s.head_dim, step.cache.block_size, s.scale, s.window)
+        if step.is_decode and rt.dtype == torch.bfloat16:
+            splits = decode_splits(n, s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16)), step.max_ctx)
+            scratch_o = scratch_ml = None
+            if splits > 1:
+                scratch_o = rt.workspace.get("attn_split_o", (n * s.num_heads * splits * s.head_dim,), torch.float32)
+                scratch_ml = rt.workspace.get("attn_split_ml", (n * s.num_heads * splits * 2,), torch.float32)
+            ops.attention_decode(q, k_cache, v_cache, table, step.ctx_after, ctx, s.num_heads, s.num_kv_heads,
+                                 s.head_dim, step.cache.block_size, s.scale, s.window, splits, scratch_o, scratch_ml)
+        else:
+            ops.attention(q, k_cache, v_cache, table, step.positions, step.token_seq, ctx, s.num_heads,
+                          s.num_kv_heads, s.head_dim, step.cache.block_size, s.scale, s.window)
         ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32)
 
 

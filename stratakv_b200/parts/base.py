@@ -98,6 +98,9 @@ class StepBatch:
 
 class Part:
     role = "part"
+    # True if forward() only launches kernels on fixed device buffers (no host reads of
+    # device data, no host-side per-sequence work), so a step can be captured in a CUDA graph.
+    graph_safe = False
 
     def __init__(self, spec, runtime: Runtime):
         self.spec = spec

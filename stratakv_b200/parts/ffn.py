@@ -25,6 +25,8 @@ def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 class GatedMlp(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         if spec.activation not in _ops.ACTIVATIONS:

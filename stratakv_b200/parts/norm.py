@@ -12,6 +12,8 @@ from .registry import register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     @classmethod
     def expected_tensors(cls, spec):
         return {spec.weight: TensorRequest((spec.size,), "around_one")}

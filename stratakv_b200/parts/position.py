@@ -32,12 +32,15 @@ class RopeHalf:
         self.rt = runtime
         self.table = None
         self.length = 0
+        self._retired = []          # earlier tables stay alive: captured graphs may still read them
 
     def ensure(self, positions: int) -> None:
         """Make the table cover positions ``0 .. positions-1`` (never inside a graph capture)."""
         if positions <= self.length:
             return
         length = max(positions, 2 * self.length, 256)
+        if self.table is not None:
+            self._retired.append(self.table)
         host = torch.from_numpy(rope_table(self.spec.head_dim, self.spec.theta, length))
         self.table = host.to(self.rt.device).contiguous()
         self.length = length

@@ -85,10 +85,10 @@ def test_groups_have_storage_of_their_own():
     cache = KVCache(requests, 6, 16, 3, torch.float32, "cpu")
     assert len(cache.groups) == 3
     assert cache.entry_group == [(0, 0), (1, 0), (0, 1), (2, 0), (-1, -1)]
-    assert cache.groups[0].keys.shape == (2, 6, 2, 16, 16) and cache.groups[2].values.shape == (1, 6, 4, 16, 32)
+    assert cache.groups[0].keys.shape == (2, 7, 2, 16, 16) and cache.groups[2].values.shape == (1, 7, 4, 16, 32)
     k0, _ = cache.entry_kv(0)
     k2, _ = cache.entry_kv(2)
-    assert k0.data_ptr() != k2.data_ptr() and k0.shape == (6, 2, 16, 16)
+    assert k0.data_ptr() != k2.data_ptr() and k0.shape == (7, 2, 16, 16)      # 6 blocks and the spare one
     with pytest.raises(KeyError):
         cache.entry_kv(4)
     slot = cache.acquire()

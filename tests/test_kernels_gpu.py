@@ -266,3 +266,61 @@ def test_argmax_lowest_index_among_equals():
     logits[2, 5] = float("nan")
     k.argmax(logits, out, flag)
     assert int(flag) & 2
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size,lengths,window,splits", [
+    (4, 2, 16, 16, [5, 40, 17, 1], 0, 1),
+    (6, 3, 48, 16, [33, 1, 100], 0, 3),
+    (32, 4, 64, 64, [700, 129, 2048, 64], 0, 8),          # the TinyLlama head layout
+    (8, 8, 128, 32, [300, 31], 0, 2),                     # no sharing of KV heads
+    (20, 1, 32, 16, [90, 45], 0, 4),                      # more than 16 query heads on one KV head
+    (4, 2, 32, 16, [90, 45, 7], 20, 2),                   # a window of 20 keys
+    (8, 2, 80, 64, [500], 0, 64),                         # more splits than there is work
+])
+def test_attention_decode(heads, kv_heads, head_dim, block_size, lengths, window, splits):
+    dtype = torch.bfloat16
+    k = lib(dtype, head_dim)
+    setup = paged_setup(dtype, lengths, [1] * len(lengths), heads, kv_heads, head_dim, block_size, seed=heads)
+    n = len(lengths)
+    out = torch.full((n, heads * head_dim), float("nan"), device="cuda").to(dtype)
+    scale = 0.37 / math.sqrt(head_dim)
+    ctx_after = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    scratch_o = torch.full((n * heads * splits * head_dim,), float("nan"), device="cuda")
+    scratch_ml = torch.full((n * heads * splits * 2,), float("nan"), device="cuda")
+    k.attention_decode(setup["q"].view(n, -1), setup["k_cache"], setup["v_cache"], setup["table"], ctx_after, out,
+                       heads, kv_heads, head_dim, block_size, scale, window, splits, scratch_o, scratch_ml)
+    ref = attention_reference(setup, dtype, heads, kv_heads, scale, window).view(n, -1)
+    close(out, ref, dtype)
+    # the general kernel gives the same answer up to rounding
+    other = torch.zeros_like(out)
+    k.attention(setup["q"].view(n, -1), setup["k_cache"], setup["v_cache"], setup["table"], setup["positions"],
+                setup["token_seq"], other, heads, kv_heads, head_dim, block_size, scale, window)
+    close(out, other, dtype)
+
+
+def test_attention_decode_finds_one_far_key_and_ignores_what_lies_beyond():
+    """One key among two thousand dominates; rows of the last block beyond the length hold
+    huge values that must not leak in."""
+    dtype, heads, kv_heads, head_dim, block_size = torch.bfloat16, 8, 2, 64, 64
+    k = lib(dtype, head_dim)
+    for far, length in ((0, 2000), (1023, 2000), (1999, 2000), (64, 65)):
+        setup = paged_setup(dtype, [length], [1], heads, kv_heads, head_dim, block_size, seed=far)
+        q = setup["q"].float()
+        key = 8.0 * q[0, 5] / q[0, 5].norm()                    # head 5 uses kv head 1
+        block = int(setup["table"][0, far // block_size])
+        setup["k_cache"][block, 1, far % block_size] = key.to(dtype)
+        setup["keys"][0][far, 1] = key.cpu()
+        last = int(setup["table"][0, (length - 1) // block_size])
+        setup["k_cache"][last, :, length % block_size:] = 100.0   # stale rows past the end
+        setup["v_cache"][last, :, length % block_size:] = 1e4
+        for splits in (1, 5):
+            out = torch.zeros(1, heads * head_dim, device="cuda").to(dtype)
+            so = torch.zeros(heads * splits * head_dim, device="cuda")
+            sm = torch.zeros(heads * splits * 2, device="cuda")
+            k.attention_decode(setup["q"].view(1, -1), setup["k_cache"], setup["v_cache"], setup["table"],
+                               torch.tensor([length], dtype=torch.int32, device="cuda"), out, heads, kv_heads,
+                               head_dim, block_size, 4.0, 0, splits, so, sm)
+            ref = attention_reference(setup, dtype, heads, kv_heads, 4.0).view(1, -1)
+            close(out, ref, dtype)
+            want = setup["values"][0][far, 1].to(dtype).float()
+            torch.testing.assert_close(out[0, 5 * head_dim:6 * head_dim].float().cpu(), want, rtol=2e-2, atol=2e-2)
