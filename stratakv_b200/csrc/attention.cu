@@ -59,6 +59,8 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  const int* __restrict__ token_seq, T* __restrict__ out, int n_tokens, int num_heads,
                  int num_kv_heads, int block_size, float scale, int window) {
     __shared__ __align__(16) float q_smem[ATT_WARPS][HD];
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * ATT_WARPS + warp;
     if (item >= (long long)n_tokens * num_heads) return;       // whole warps leave together
@@ -132,8 +134,8 @@ SKV_EXPORT int skv_attention(const void* q, const void* k_cache, const void* v_c
     const long long items = (long long)n_tokens * num_heads;
     const long long blocks = (items + ATT_WARPS - 1) / ATT_WARPS;
     if (blocks > 0x7fffffffLL) return fail("skv_attention", "too many tokens in one step");
-    attention_kernel<skv_t><<<(unsigned)blocks, ATT_WARPS * 32, 0, stream>>>(
-        (const skv_t*)q, (const skv_t*)k_cache, (const skv_t*)v_cache, block_table, table_width, positions,
-        token_seq, (skv_t*)out, n_tokens, num_heads, num_kv_heads, block_size, scale, window);
-    return check_launch("skv_attention");
+    return launch_pdl("skv_attention", attention_kernel<skv_t>, dim3((unsigned)blocks), dim3(ATT_WARPS * 32), 0,
+                      stream, (const skv_t*)q, (const skv_t*)k_cache, (const skv_t*)v_cache, block_table,
+                      table_width, positions, token_seq, (skv_t*)out, n_tokens, num_heads, num_kv_heads,
+                      block_size, scale, window);
 }

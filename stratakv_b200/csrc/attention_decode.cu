@@ -51,6 +51,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         int num_kv_heads, int block_size, float scale, int window, int splits, int m_tiles) {
     extern __shared__ float merge[];                  // [warps][16][DHD + 2]
     constexpr int PITCH = DHD + 2;
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tig = lane & 3;
     const int seq = blockIdx.x;
@@ -217,6 +219,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 // out[seq, head, :] = sum_s e^(m_s - M) O_s / sum_s e^(m_s - M) l_s
 __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                       __nv_bfloat16* __restrict__ out, int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t item = blockIdx.x;                   // seq * num_heads + head
     float m = -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, partial_ml[2 * (item * splits + s)]);
@@ -267,16 +271,16 @@ SKV_EXPORT int skv_attention_decode(const void* q, const void* k_cache, const vo
         configured = true;
     }
     dim3 grid(n_seqs, num_kv_heads * m_tiles, splits);
-    decode_attention_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
-        table_width, ctx_after, (__nv_bfloat16*)out, partial_o, partial_ml, num_heads, num_kv_heads, block_size,
-        scale, window, splits, m_tiles);
-    if (int code = check_launch("skv_attention_decode")) return code;
-    if (splits > 1) {
-        decode_combine_kernel<<<n_seqs * num_heads, DHD >= 128 ? 128 : 64, 0, stream>>>(
-            partial_o, partial_ml, (__nv_bfloat16*)out, splits);
-        return check_launch("skv_attention_decode(combine)");
-    }
+    if (int code = launch_pdl("skv_attention_decode", decode_attention_kernel, grid, dim3(DEC_WARPS * 32), smem,
+                              stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+                              (const __nv_bfloat16*)v_cache, block_table, table_width, ctx_after,
+                              (__nv_bfloat16*)out, partial_o, partial_ml, num_heads, num_kv_heads, block_size,
+                              scale, window, splits, m_tiles))
+        return code;
+    if (splits > 1)
+        return launch_pdl("skv_attention_decode(combine)", decode_combine_kernel, dim3(n_seqs * num_heads),
+                          dim3(DHD >= 128 ? 128 : 64), 0, stream, (const float*)partial_o,
+                          (const float*)partial_ml, (__nv_bfloat16*)out, splits);
     return 0;
 }
 

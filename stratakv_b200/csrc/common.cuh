@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 
 #define SKV_F32 0
 #define SKV_BF16 1
@@ -44,6 +45,42 @@ inline int fail(const char* what, const char* detail = "") {
 inline int check_launch(const char* kernel) {
     cudaError_t status = cudaGetLastError();
     if (status != cudaSuccess) return fail(kernel, cudaGetErrorString(status));
+    return 0;
+}
+
+// ---- programmatic dependent launch ------------------------------------------
+// Kernels of a step are launched so that the next one may start while the
+// previous one drains: it can fetch what does not depend on its predecessor
+// (weights, tables) and then waits.  pdl_wait() returns once the preceding
+// kernel on the stream has completed and its writes are visible; nothing that a
+// predecessor writes may be read, and nothing a predecessor reads may be
+// written, before it.  Set SKV_NO_PDL=1 in the environment to launch plainly.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+inline bool pdl_enabled() {
+    static const bool enabled = [] {
+        const char* off = getenv("SKV_NO_PDL");
+        return !(off && off[0] == '1');
+    }();
+    return enabled;
+}
+
+template <typename... KernelArgs, typename... Args>
+inline int launch_pdl(const char* name, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                      cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl_enabled() ? 1 : 0;
+    const cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+    if (status != cudaSuccess) return fail(name, cudaGetErrorString(status));
     return 0;
 }
 

@@ -16,6 +16,8 @@ namespace skv {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int hidden, int vocab, int* __restrict__ flag) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* row_out = out + (size_t)t * hidden;
@@ -36,6 +38,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                float eps, T* __restrict__ out, const int* __restrict__ rows,
                                int hidden) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     const float* row = x + (size_t)src * hidden;
@@ -64,6 +68,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
                                      T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      int num_heads, int num_kv_heads, int head_dim, int block_size,
                                      int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = head_dim >> 1;
     const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
@@ -124,8 +130,8 @@ SKV_EXPORT int skv_embed(const void* table, const int* ids, float* out, int n_to
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) return fail("skv_embed", "hidden and vocab must be positive");
     const int threads = hidden >= 1024 ? 256 : 128;
-    embed_kernel<skv_t><<<n_tokens, threads, 0, stream>>>((const skv_t*)table, ids, out, hidden, vocab, flag);
-    return check_launch("skv_embed");
+    return launch_pdl("skv_embed", embed_kernel<skv_t>, dim3(n_tokens), dim3(threads), 0, stream,
+                      (const skv_t*)table, ids, out, hidden, vocab, flag);
 }
 
 SKV_EXPORT int skv_rmsnorm(const float* x, const float* gamma, float eps, void* out, const int* rows,
@@ -133,8 +139,8 @@ SKV_EXPORT int skv_rmsnorm(const float* x, const float* gamma, float eps, void* 
     if (n_rows <= 0) return 0;
     if (hidden <= 0) return fail("skv_rmsnorm", "hidden must be positive");
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    rmsnorm_kernel<skv_t><<<n_rows, threads, 0, stream>>>(x, gamma, eps, (skv_t*)out, rows, hidden);
-    return check_launch("skv_rmsnorm");
+    return launch_pdl("skv_rmsnorm", rmsnorm_kernel<skv_t>, dim3(n_rows), dim3(threads), 0, stream, x, gamma, eps,
+                      (skv_t*)out, rows, hidden);
 }
 
 SKV_EXPORT int skv_rope_kv_write(const float* qkv, const float* cos_sin, const int* positions,
@@ -146,10 +152,9 @@ SKV_EXPORT int skv_rope_kv_write(const float* qkv, const float* cos_sin, const i
     if (head_dim <= 0 || (head_dim & 1)) return fail("skv_rope_kv_write", "head_dim must be positive and even");
     if (num_heads <= 0 || num_kv_heads <= 0 || block_size <= 0)
         return fail("skv_rope_kv_write", "head counts and block_size must be positive");
-    rope_kv_write_kernel<skv_t><<<n_tokens, 128, 0, stream>>>(
-        qkv, (const float2*)cos_sin, positions, token_seq, block_table, table_width, (skv_t*)q_out,
-        (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv);
-    return check_launch("skv_rope_kv_write");
+    return launch_pdl("skv_rope_kv_write", rope_kv_write_kernel<skv_t>, dim3(n_tokens), dim3(128), 0, stream, qkv,
+                      (const float2*)cos_sin, positions, token_seq, block_table, table_width, (skv_t*)q_out,
+                      (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv);
 }
 
 SKV_EXPORT int skv_add_inplace(float* out, const float* in, long long n, cudaStream_t stream) {

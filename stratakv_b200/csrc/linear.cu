@@ -55,6 +55,8 @@ linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void
                   int M, int N, int K, int mode, int act) {
     __shared__ float As[FBK][FBM + 4];
     __shared__ float Ws[FBK][FBN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * FBM, n0 = blockIdx.x * FBN;
@@ -107,10 +109,11 @@ linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void
 }
 
 static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                         cudaStream_t stream) {
+                         int* flag, cudaStream_t stream) {
+    (void)flag;
     dim3 grid((N + FBN - 1) / FBN, (M + FBM - 1) / FBM);
-    linear_f32_kernel<<<grid, 256, 0, stream>>>((const float*)a, (const float*)w, out, M, N, K, mode, act);
-    return check_launch("skv_linear(float)");
+    return launch_pdl("skv_linear(float)", linear_f32_kernel, grid, dim3(256), 0, stream, (const float*)a,
+                      (const float*)w, out, M, N, K, mode, act);
 }
 
 #else  // bfloat16
@@ -132,12 +135,15 @@ __device__ __forceinline__ uint4 load_weight16(const uint4* p) {
 // One block owns 16 rows of W and one chunk of 8*TG tokens.  Its warps take the
 // 32-wide k steps round robin, then their partial tiles are summed in shared
 // memory in warp order (a fixed order: results do not depend on timing).
-template <int TG, bool STREAM>
-__global__ void __launch_bounds__(256)
+// Weights do not depend on the kernel before this one, so the first batch of
+// weight loads is issued before pdl_wait(): it overlaps the predecessor's tail.
+template <int TG, int U, bool STREAM, int MAX_WARPS>
+__global__ void __launch_bounds__(MAX_WARPS * 32)
 skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                           void* __restrict__ out, int M, int N, int K, int mode, int act) {
     extern __shared__ float red[];                 // [warps][16][8*TG + 1]
     constexpr int COLS = 8 * TG, PITCH = COLS + 1;
+    pdl_launch_dependents();
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tig = lane & 3;
@@ -148,6 +154,21 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
     const bool has_a = n0 + g < N, has_b = n0 + g + 8 < N;
     const __nv_bfloat16* wa_ptr = W + (size_t)row_a * K + tig * 8;
     const __nv_bfloat16* wb_ptr = W + (size_t)row_b * K + tig * 8;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    uint4 wa[U], wb[U];
+    auto load_weights = [&](int s0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (s0 + u * warps) << 5;
+            const bool live = (s0 + u * warps) < steps && (k + tig * 8) < K;
+            wa[u] = (live && has_a) ? load_weight16<STREAM>((const uint4*)(wa_ptr + k)) : zero;
+            wb[u] = (live && has_b) ? load_weight16<STREAM>((const uint4*)(wb_ptr + k)) : zero;
+        }
+    };
+    load_weights(warp);
+    pdl_wait();                                    // activations (and the residual stream) are ready now
+
     const __nv_bfloat16* x_ptr[TG];
     bool has_x[TG];
 #pragma unroll
@@ -160,17 +181,8 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
 #pragma unroll
     for (int t = 0; t < TG; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f; }
 
-    constexpr int U = 4;
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     for (int s0 = warp; s0 < steps; s0 += warps * U) {
-        uint4 wa[U], wb[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int k = (s0 + u * warps) << 5;
-            const bool live = (s0 + u * warps) < steps && (k + tig * 8) < K;
-            wa[u] = (live && has_a) ? load_weight16<STREAM>((const uint4*)(wa_ptr + k)) : zero;
-            wb[u] = (live && has_b) ? load_weight16<STREAM>((const uint4*)(wb_ptr + k)) : zero;
-        }
+        if (s0 != warp) load_weights(s0);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (s0 + u * warps) << 5;
@@ -218,36 +230,51 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
     }
 }
 
-template <int TG>
+template <int TG, int U, int MAX_WARPS>
 static int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                          cudaStream_t stream) {
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
     const int steps = (K + 31) / 32;
-    // Enough warps to keep loads in flight on 148 SMs, never more than k steps.
-    int warps = 8;
-    if ((long long)row_tiles * chunks >= 148 * 4) warps = 4;
+    // Few row tiles: many warps per block so that enough loads are in flight on each SM;
+    // many row tiles: several smaller blocks per SM do the same.  Never more warps than k steps.
+    const long long blocks = (long long)row_tiles * chunks;
+    int warps = blocks >= 148 * 4 ? 4 : 8;
+    if (warps > MAX_WARPS) warps = MAX_WARPS;
     while (warps > 1 && warps > steps) warps >>= 1;
     const size_t smem = (size_t)warps * 16 * (8 * TG + 1) * sizeof(float);
     dim3 grid(row_tiles, chunks);
     if (chunks == 1)
-        skinny_linear_bf16_kernel<TG, true><<<grid, warps * 32, smem, stream>>>(
-            (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K, mode, act);
-    else
-        skinny_linear_bf16_kernel<TG, false><<<grid, warps * 32, smem, stream>>>(
-            (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K, mode, act);
-    return check_launch("skv_linear(bfloat16)");
+        return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, true, MAX_WARPS>, grid, dim3(warps * 32),
+                          smem, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K, mode, act);
+    return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, false, MAX_WARPS>, grid, dim3(warps * 32), smem,
+                      stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K, mode, act);
+}
+
+// gemm_tcgen05.cu: the tensor-memory GEMM that serves steps with many tokens
+int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
+                   cudaStream_t stream);
+
+static bool tcgen05_enabled() {
+    static const bool enabled = [] {
+        const char* off = getenv("SKV_NO_TCGEN05");
+        return !(off && off[0] == '1');
+    }();
+    return enabled;
 }
 
 static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                         cudaStream_t stream) {
+                         int* flag, cudaStream_t stream) {
     if (K % 8 != 0)
         return fail("skv_linear(bfloat16)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15)
         return fail("skv_linear(bfloat16)", "operands must be 16-byte aligned");
-    if (M <= 8) return launch_skinny<1>(a, w, out, M, N, K, mode, act, stream);
-    if (M <= 16) return launch_skinny<2>(a, w, out, M, N, K, mode, act, stream);
-    if (M <= 32) return launch_skinny<4>(a, w, out, M, N, K, mode, act, stream);
-    return launch_skinny<8>(a, w, out, M, N, K, mode, act, stream);
+    if (M > 64 && tcgen05_enabled()) return linear_tcgen05(a, w, out, M, N, K, mode, flag, stream);
+    // at most 8 warps and under 100 registers a thread: two blocks fit on an SM, so the next
+    // kernel's weight loads are in flight while this one finishes
+    if (M <= 8) return launch_skinny<1, 8, 8>(a, w, out, M, N, K, mode, act, stream);
+    if (M <= 16) return launch_skinny<2, 8, 8>(a, w, out, M, N, K, mode, act, stream);
+    if (M <= 32) return launch_skinny<4, 4, 8>(a, w, out, M, N, K, mode, act, stream);
+    return launch_skinny<8, 4, 8>(a, w, out, M, N, K, mode, act, stream);
 }
 #endif
 
@@ -255,13 +282,14 @@ static int launch_linear(const void* a, const void* w, void* out, int M, int N, 
 
 using namespace skv;
 
+// `flag` (may be null): bit 2 (value 4) is raised if a pipeline wait inside a kernel timed out.
 SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                          cudaStream_t stream) {
+                          int* flag, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (N <= 0 || K <= 0) return fail("skv_linear", "N and K must be positive");
     if (mode < 0 || mode > 3) return fail("skv_linear", "unknown epilogue mode");
     if (mode == MODE_GATED && N % 16 != 0)
         return fail("skv_linear", "a gated weight must have a multiple of 16 rows (gate/up tiles of 8)");
     if (act != ACT_SILU) return fail("skv_linear", "unknown activation");
-    return launch_linear(a, w, out, M, N, K, mode, act, stream);
+    return launch_linear(a, w, out, M, N, K, mode, act, flag, stream);
 }

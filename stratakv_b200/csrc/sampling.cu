@@ -14,14 +14,25 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
                               int* __restrict__ flag) {
     __shared__ float best_value[32];
     __shared__ int best_index[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * vocab;
     float value = -INFINITY;
     int index = 0x7fffffff;
     bool bad = false;
-    for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
-        const float v = row[c];
+    auto consider = [&](float v, int c) {
         if (!isfinite(v)) bad = true;
         if (v > value || (v == value && c < index)) { value = v; index = c; }
+    };
+    if ((((uintptr_t)row) & 15) == 0) {
+        const int quads = vocab >> 2;
+        for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+            const float4 v = ((const float4*)row)[i];
+            consider(v.x, 4 * i); consider(v.y, 4 * i + 1); consider(v.z, 4 * i + 2); consider(v.w, 4 * i + 3);
+        }
+        for (int c = (quads << 2) + threadIdx.x; c < vocab; c += blockDim.x) consider(row[c], c);
+    } else {
+        for (int c = threadIdx.x; c < vocab; c += blockDim.x) consider(row[c], c);
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
 #pragma unroll
@@ -57,8 +68,7 @@ using namespace skv;
 SKV_EXPORT int skv_argmax(const float* logits, int* out, int rows, int vocab, int* flag, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return fail("skv_argmax", "vocab must be positive");
-    argmax_kernel<<<rows, 256, 0, stream>>>(logits, out, vocab, flag);
-    return check_launch("skv_argmax");
+    return launch_pdl("skv_argmax", argmax_kernel, dim3(rows), dim3(1024), 0, stream, logits, out, vocab, flag);
 }
 
 // ---------------------------------------------------------------------------
@@ -170,6 +180,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     __shared__ unsigned long long chunk_sum[SAMPLE_THREADS];
     __shared__ float scratch[33];
     __shared__ int bad_flag;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * vocab;
     if (threadIdx.x == 0) bad_flag = 0;
     __syncthreads();
@@ -280,7 +292,6 @@ SKV_EXPORT int skv_sample(const float* logits, int* out, int rows, int vocab, fl
         return fail("skv_sample", "temperature must be positive and finite (0 is greedy: use skv_argmax)");
     if (top_k < 0) return fail("skv_sample", "top_k must be non-negative");
     if (!(top_p > 0.0f) || top_p > 1.0f) return fail("skv_sample", "top_p must be in (0, 1]");
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab, temperature, top_k, top_p, seed,
-                                                       streams, counters, flag);
-    return check_launch("skv_sample");
+    return launch_pdl("skv_sample", sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, out, vocab,
+                      temperature, top_k, top_p, (unsigned long long)seed, streams, counters, flag);
 }

@@ -16,6 +16,8 @@ what varies per step (positions, lengths, tables) is read from device memory.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, List, Sequence
 
 import numpy as np
@@ -36,7 +38,7 @@ def bucket_for(batch: int) -> int:
 
 class DecodeGraph:
     def __init__(self, engine, bucket: int, width: int):
-        self.engine = engine
+        self._engine = weakref.ref(engine)     # no reference cycle: an engine is freed when dropped
         self.bucket = bucket
         self.width = width
         cache = engine.cache
@@ -73,6 +75,10 @@ class DecodeGraph:
         self.graph = None
         self.logits = None
         self.kernels_per_replay = 0
+
+    @property
+    def engine(self):
+        return self._engine()
 
     def _np(self, name):
         start, count = self.offsets[name]
@@ -131,8 +137,17 @@ class DecodeGraph:
                 torch.cuda.synchronize(engine.device)
                 before = engine.kernel_launches()
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    self.logits = engine.model.forward(self.step, self.want_rows, self.bucket)
+                # Garbage collection inside a capture could destroy another engine's graph,
+                # which is not allowed while a stream captures.
+                gc.collect()
+                was_enabled = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(graph):
+                        self.logits = engine.model.forward(self.step, self.want_rows, self.bucket)
+                finally:
+                    if was_enabled:
+                        gc.enable()
                 self.kernels_per_replay = engine.kernel_launches() - before
                 engine.discount_launches(self.kernels_per_replay)       # recorded, not run
                 self.graph = graph

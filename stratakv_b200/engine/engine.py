@@ -285,7 +285,13 @@ class Engine:
     def check_flags(self) -> None:
         """Raise if a kernel flagged bad input since the last check (reads one word from the device)."""
         flags = int(self.model.flags.item())
+        for kernels in _ops._LOADED.values():
+            if kernels.error_flag is not None:
+                word = int(kernels.error_flag.item())
+                if word:
+                    kernels.error_flag.zero_()
+                    flags |= word
         if flags:
             self.model.flags.zero_()
             raise StepError(f"device flags raised: {flags:#x} (1: token id outside the vocabulary, "
-                            "2: non-finite logits)")
+                            "2: non-finite logits, 4: a wait inside a kernel timed out)")

@@ -51,6 +51,8 @@ class Kernels:
         self.lib.skv_last_error.restype = ctypes.c_char_p
         if self.lib.skv_library_head_dim() != head_dim:
             raise KernelError(f"{self.path} was built for another head size")
+        # A device word kernels raise bits in (4: a pipeline wait inside a kernel timed out).
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device="cuda") if torch.cuda.is_available() else None
 
     # ---- helpers -----------------------------------------------------------
     def _check(self, code: int, name: str) -> None:
@@ -95,7 +97,7 @@ class Kernels:
         self._check(self.lib.skv_rmsnorm(_ptr(x), _ptr(gamma), ctypes.c_float(eps), _ptr(out), _ptr(rows),
                                          n_rows, hidden, _stream()), "rmsnorm")
 
-    def linear(self, a, w, out, mode: int = MODE_STORE, activation: str = "silu"):
+    def linear(self, a, w, out, mode: int = MODE_STORE, activation: str = "silu", flag=None):
         """out = a[M,K] . w[N,K]^T with the epilogue ``mode``."""
         self._want(a, self.dtype, "a"); self._want(w, self.dtype, "w")
         M, K = a.shape
@@ -110,7 +112,7 @@ class Kernels:
         if activation not in ACTIVATIONS:
             raise KernelError(f"linear: unknown activation '{activation}'")
         self._check(self.lib.skv_linear(_ptr(a), _ptr(w), _ptr(out), M, N, K, mode, ACTIVATIONS[activation],
-                                        _stream()), "linear")
+                                        _ptr(flag if flag is not None else self.error_flag), _stream()), "linear")
 
     def rope_kv_write(self, qkv, cos_sin, positions, token_seq, block_table, q_out, k_cache, v_cache,
                       num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, write_kv: bool):
