@@ -84,6 +84,8 @@ inline int launch_pdl(const char* name, void (*kernel)(KernelArgs...), dim3 grid
     return 0;
 }
 
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -324,3 +324,56 @@ def test_attention_decode_finds_one_far_key_and_ignores_what_lies_beyond():
             close(out, ref, dtype)
             want = setup["values"][0][far, 1].to(dtype).float()
             torch.testing.assert_close(out[0, 5 * head_dim:6 * head_dim].float().cpu(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size,lengths,new,window", [
+    (4, 2, 16, 16, [5, 40, 17], [5, 40, 17], 0),
+    (6, 3, 48, 16, [33, 1, 100, 64], [33, 1, 100, 64], 0),
+    (32, 4, 64, 64, [300, 129, 65], [300, 129, 65], 0),       # the TinyLlama head layout
+    (8, 1, 64, 64, [70, 200], [6, 65], 0),                    # continuing prompts that are partly cached
+    (5, 5, 128, 32, [130], [130], 0),
+    (3, 3, 80, 64, [97, 31], [97, 30], 0),
+    (4, 2, 32, 16, [150, 45], [150, 20], 20),                 # a window of 20 keys
+    (4, 4, 32, 16, [200], [100], 70),                         # a window wider than a key tile
+])
+def test_attention_prefill(heads, kv_heads, head_dim, block_size, lengths, new, window):
+    dtype = torch.bfloat16
+    k = lib(dtype, head_dim)
+    assert k.has_attention_prefill()
+    setup = paged_setup(dtype, lengths, new, heads, kv_heads, head_dim, block_size, seed=heads + head_dim)
+    n = setup["q"].shape[0]
+    out = torch.full((n, heads * head_dim), float("nan"), device="cuda").to(dtype)
+    scale = 0.37 / math.sqrt(head_dim)
+    cu_q = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device="cuda")
+    ctx_after = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    k.attention_prefill(setup["q"].view(n, -1), setup["k_cache"], setup["v_cache"], setup["table"], cu_q, ctx_after,
+                        out, max(new), heads, kv_heads, head_dim, block_size, scale, window)
+    ref = attention_reference(setup, dtype, heads, kv_heads, scale, window).view(n, -1)
+    close(out, ref, dtype)
+
+
+def test_attention_prefill_at_the_edges_of_tiles_and_windows():
+    """Make single keys dominate at places where masks and tiles meet: the causal edge
+    (the query's own key), the key before a tile boundary, the first key inside a window and
+    the last one outside it (which must not be seen)."""
+    dtype, heads, kv_heads, head_dim, block_size = torch.bfloat16, 2, 1, 32, 16
+    k = lib(dtype, head_dim)
+    length, window = 160, 48
+    for query, far, visible in ((100, 100, True), (100, 63, True), (100, 64, True), (100, 53, True),
+                                (100, 52, False), (128, 81, True), (128, 80, False), (159, 0, False)):
+        setup = paged_setup(dtype, [length], [length], heads, kv_heads, head_dim, block_size, seed=query + far)
+        q = setup["q"].float()
+        key = 9.0 * q[query, 1] / q[query, 1].norm()
+        block = int(setup["table"][0, far // block_size])
+        setup["k_cache"][block, 0, far % block_size] = key.to(dtype)
+        setup["keys"][0][far, 0] = key.cpu()
+        out = torch.zeros(length, heads * head_dim, device="cuda").to(dtype)
+        cu_q = torch.tensor([0, length], dtype=torch.int32, device="cuda")
+        ctx_after = torch.tensor([length], dtype=torch.int32, device="cuda")
+        k.attention_prefill(setup["q"].view(length, -1), setup["k_cache"], setup["v_cache"], setup["table"], cu_q,
+                            ctx_after, out, length, heads, kv_heads, head_dim, block_size, 4.0, window)
+        ref = attention_reference(setup, dtype, heads, kv_heads, 4.0, window).view(length, -1)
+        close(out, ref, dtype)
+        got = out[query, head_dim:].float().cpu()
+        want = setup["values"][0][far, 0].to(dtype).float()
+        assert torch.allclose(got, want, rtol=2e-2, atol=2e-2) == visible
