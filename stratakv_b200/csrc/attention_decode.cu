@@ -284,11 +284,103 @@ SKV_EXPORT int skv_attention_decode(const void* q, const void* k_cache, const vo
     return 0;
 }
 
+// ---------------------------------------------------------------------------
+// skv_attention_decode_no_alloc: the same split decode attention for callers that cannot
+// allocate device memory (declared in stratakv_no_alloc.h; it has no counterpart in the
+// reference).  The partial results of the context splits live in a fixed array that is part of
+// this library's device image instead of in memory the caller hands in.
+namespace skv {
+
+// Floats of scratch held by every GPU that loads this library, until the process exits
+// (4.5 MiB).  A call needs n_seqs * heads * splits * (head_dim + 2) of them.
+constexpr size_t NO_ALLOC_SCRATCH_FLOATS = (size_t)9 << 17;
+static __device__ __align__(256) float g_no_alloc_scratch[NO_ALLOC_SCRATCH_FLOATS];
+
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+
+}  // namespace skv
+
+SKV_EXPORT long long skv_attention_decode_no_alloc_capacity() { return (long long)NO_ALLOC_SCRATCH_FLOATS; }
+
+SKV_EXPORT int skv_attention_decode_no_alloc(const void* q, const void* k_cache, const void* v_cache,
+                                             const int* block_table, int table_width, const int* ctx_after,
+                                             void* out, int n_seqs, int num_heads, int num_kv_heads,
+                                             int head_dim, int block_size, float scale, int window, int splits,
+                                             cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (head_dim != DHD) return fail("skv_attention_decode_no_alloc", "this library was built for another head size");
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
+        return fail("skv_attention_decode_no_alloc", "heads must be a positive multiple of kv heads");
+    if (block_size <= 0 || block_size % 16 != 0)
+        return fail("skv_attention_decode_no_alloc", "block_size must be a positive multiple of 16");
+    if (splits < 1 || splits > 65535) return fail("skv_attention_decode_no_alloc", "bad number of splits");
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15)
+        return fail("skv_attention_decode_no_alloc", "operands must be 16-byte aligned");
+    const size_t slots = (size_t)n_seqs * num_heads * splits;
+    const size_t needed = slots * (DHD + 2);
+    if (needed > NO_ALLOC_SCRATCH_FLOATS) {
+        char detail[256];
+        snprintf(detail, sizeof detail,
+                 "n_seqs * heads * splits * (head_dim + 2) = %zu floats of scratch are needed, the built-in "
+                 "array holds %zu: use fewer splits or sequences per call",
+                 needed, (size_t)NO_ALLOC_SCRATCH_FLOATS);
+        return fail("skv_attention_decode_no_alloc", detail);
+    }
+    // In host code the array's name is a stand-in, not a device address.  The address the kernel
+    // needs is asked for once per device, with that device current (the first call on a device
+    // does it, which is why that call should come before any stream capture).
+    static float* scratch_of_device[NO_ALLOC_MAX_DEVICES] = {nullptr};
+    static bool attribute_set[NO_ALLOC_MAX_DEVICES] = {false};
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return fail("skv_attention_decode_no_alloc", cudaGetErrorString(status));
+    if (device < 0 || device >= NO_ALLOC_MAX_DEVICES)
+        return fail("skv_attention_decode_no_alloc", "device index is beyond what this entry point tracks");
+    if (!scratch_of_device[device]) {
+        float* address = nullptr;
+        status = cudaGetSymbolAddress((void**)&address, g_no_alloc_scratch);
+        if (status != cudaSuccess) return fail("skv_attention_decode_no_alloc(cudaGetSymbolAddress)", cudaGetErrorString(status));
+        if (!address) return fail("skv_attention_decode_no_alloc", "cudaGetSymbolAddress returned no address");
+        scratch_of_device[device] = address;
+    }
+    float* partial_o = scratch_of_device[device];
+    float* partial_ml = partial_o + slots * DHD;
+    const int group_size = num_heads / num_kv_heads;
+    const int m_tiles = (group_size + 15) / 16;
+    const size_t smem = (size_t)DEC_WARPS * 16 * (DHD + 2) * sizeof(float);
+    if (!attribute_set[device]) {
+        status = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("skv_attention_decode_no_alloc", cudaGetErrorString(status));
+        attribute_set[device] = true;
+    }
+    // Every slot that the combine step reads is written by exactly one block of the first kernel
+    // (a split without keys writes an empty partial), so nothing of the array has to start at zero.
+    dim3 grid(n_seqs, num_kv_heads * m_tiles, splits);
+    if (int code = launch_pdl("skv_attention_decode_no_alloc", decode_attention_kernel, grid, dim3(DEC_WARPS * 32),
+                              smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+                              (const __nv_bfloat16*)v_cache, block_table, table_width, ctx_after,
+                              (__nv_bfloat16*)out, partial_o, partial_ml, num_heads, num_kv_heads, block_size,
+                              scale, window, splits, m_tiles))
+        return code;
+    if (splits > 1)
+        return launch_pdl("skv_attention_decode_no_alloc(combine)", decode_combine_kernel,
+                          dim3(n_seqs * num_heads), dim3(DHD >= 128 ? 128 : 64), 0, stream,
+                          (const float*)partial_o, (const float*)partial_ml, (__nv_bfloat16*)out, splits);
+    return 0;
+}
+
 #else
 
 SKV_EXPORT int skv_attention_decode(const void*, const void*, const void*, const int*, int, const int*, void*,
                                     float*, float*, int, int, int, int, int, float, int, int, cudaStream_t) {
     return skv::fail("skv_attention_decode", "the float32 build decodes with skv_attention");
+}
+
+SKV_EXPORT long long skv_attention_decode_no_alloc_capacity() { return 0; }
+
+SKV_EXPORT int skv_attention_decode_no_alloc(const void*, const void*, const void*, const int*, int, const int*, void*,
+                                             int, int, int, int, int, float, int, int, cudaStream_t) {
+    return skv::fail("skv_attention_decode_no_alloc", "only the bfloat16 build has this kernel");
 }
 
 #endif
