@@ -64,6 +64,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+
+// out[tile] += tile, done by the copy engine in L2: nothing of `out` is read into the SM
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+
+// One 16-byte piece of a thread's 128-byte output row, at its 128-byte-swizzled place in the slab
+__device__ __forceinline__ void slab_write(uint8_t* slab, int row, int piece, uint4 value) {
+    *(uint4*)(slab + row * 128 + ((piece ^ (row & 7)) << 4)) = value;
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
 // start address / 16 in bits 0-13, leading offset (unused here) 1 in bits 16-29, 1024 bytes
 // between 8-row groups / 16 in bits 32-45, descriptor version 1 in bits 46-47, swizzle mode 2
@@ -118,7 +134,8 @@ __device__ __forceinline__ float silu_gate(float g) {
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    void* __restrict__ out, int M, int N, int K, int mode, int* __restrict__ flag) {
+                    const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
+                    int N, int K, int mode, int* __restrict__ flag) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
@@ -190,7 +207,79 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quarter = warp & 3;             // the TMEM lanes this warp may read
         const int m = m0 + quarter * 32 + lane;
-        if (ok) {
+        if (ok && tma_out) {
+            // Each thread builds 128 bytes of its output row in a swizzled slab of shared memory (the
+            // pipeline's first stage is free by now); one lane hands the warp's 32 x 128-byte slab to the
+            // copy engine, which writes whole rows (or adds them, for the residual) and clips at M and N.
+            // Two slabs per warp alternate so that one is written while the other is being read.
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            uint8_t* slabs = tiles + quarter * 8192;
+            const int y = m0 + quarter * 32;
+            // accumulator columns that make one 128-byte output row, and output columns per slab
+            const int acc_per_slab = mode == TC_MODE_GATED ? 128 : (mode == TC_MODE_STORE ? 64 : 32);
+            const int out_per_slab = mode == TC_MODE_STORE_F32 || mode == TC_MODE_ADD_F32 ? 32 : 64;
+            const int out_x0 = mode == TC_MODE_GATED ? (n0 >> 1) : n0;
+            int buffer = 0;
+#pragma unroll 1
+            for (int seg = 0; seg * acc_per_slab < BN; ++seg) {
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                __syncwarp();
+                uint8_t* slab = slabs + buffer * 4096;
+#pragma unroll 1
+                for (int sub = 0; sub * 32 < acc_per_slab; ++sub) {
+                    uint32_t v[32];
+                    tmem_load_32(lane_base + (uint32_t)(seg * acc_per_slab + sub * 32), v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (mode == TC_MODE_GATED) {
+                        // 32 accumulator columns = two groups of (8 gate, 8 up) -> 16 outputs = 2 pieces
+#pragma unroll
+                        for (int grp = 0; grp < 2; ++grp) {
+                            uint32_t packed[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float lo = silu_gate(__uint_as_float(v[16 * grp + 2 * j])) *
+                                                 __uint_as_float(v[16 * grp + 8 + 2 * j]);
+                                const float hi = silu_gate(__uint_as_float(v[16 * grp + 2 * j + 1])) *
+                                                 __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
+                                const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+                                packed[j] = *(const uint32_t*)&pair;
+                            }
+                            slab_write(slab, lane, sub * 2 + grp, make_uint4(packed[0], packed[1], packed[2], packed[3]));
+                        }
+                    } else if (mode == TC_MODE_STORE) {
+#pragma unroll
+                        for (int piece = 0; piece < 4; ++piece) {
+                            uint32_t packed[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __nv_bfloat162 pair = __floats2bfloat162_rn(
+                                    __uint_as_float(v[8 * piece + 2 * e]), __uint_as_float(v[8 * piece + 2 * e + 1]));
+                                packed[e] = *(const uint32_t*)&pair;
+                            }
+                            slab_write(slab, lane, sub * 4 + piece, make_uint4(packed[0], packed[1], packed[2], packed[3]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int piece = 0; piece < 8; ++piece)
+                            slab_write(slab, lane, piece, make_uint4(v[4 * piece], v[4 * piece + 1], v[4 * piece + 2], v[4 * piece + 3]));
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    const int x = out_x0 + seg * out_per_slab;
+                    const int out_cols = mode == TC_MODE_GATED ? (N >> 1) : N;
+                    if (x < out_cols && y < M) {             // a slab wholly outside the matrix is not sent
+                        if (mode == TC_MODE_ADD_F32) tma_reduce_add_2d(&map_out, x, y, smem_addr(slab));
+                        else tma_store_2d(&map_out, x, y, smem_addr(slab));
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                buffer ^= 1;
+            }
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            __syncwarp();
+        } else if (ok) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t v[32];
@@ -204,23 +293,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)m * half_n + (n >> 1);
 #pragma unroll
                     for (int grp = 0; grp < 2; ++grp) {
-                        if (n + 16 * grp >= N) break;
-                        __align__(16) __nv_bfloat16 r[8];
+                        if (n + 16 * grp < N) {
+                            uint32_t packed[4];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            r[j] = __float2bfloat16_rn(silu_gate(__uint_as_float(v[16 * grp + j])) *
-                                                       __uint_as_float(v[16 * grp + 8 + j]));
-                        *(uint4*)(dst + 8 * grp) = *(const uint4*)r;
+                            for (int j = 0; j < 4; ++j) {
+                                const float lo = silu_gate(__uint_as_float(v[16 * grp + 2 * j])) *
+                                                 __uint_as_float(v[16 * grp + 8 + 2 * j]);
+                                const float hi = silu_gate(__uint_as_float(v[16 * grp + 2 * j + 1])) *
+                                                 __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
+                                const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+                                packed[j] = *(const uint32_t*)&pair;
+                            }
+                            *(uint4*)(dst + 8 * grp) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        }
                     }
                 } else if (mode == TC_MODE_STORE) {
                     __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)m * N + n;
                     if (n + 32 <= N && (N & 7) == 0) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
-                            __align__(16) __nv_bfloat16 r[8];
+                            uint32_t packed[4];
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) r[e] = __float2bfloat16_rn(__uint_as_float(v[j + e]));
-                            *(uint4*)(dst + j) = *(const uint4*)r;
+                            for (int e = 0; e < 4; ++e) {
+                                const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]),
+                                                                                  __uint_as_float(v[j + 2 * e + 1]));
+                                packed[e] = *(const uint32_t*)&pair;
+                            }
+                            *(uint4*)(dst + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                         }
                     } else {
                         for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
@@ -229,15 +328,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     float* dst = (float*)out + (size_t)m * N + n;
                     const bool add = mode == TC_MODE_ADD_F32;
                     if (n + 32 <= N && (N & 3) == 0) {
+                        // all old values are fetched before anything is stored: a store between two
+                        // loads of the same array would make each load wait for the one before
+                        float4 old[8];
+                        if (add) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 r = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                                   __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                            if (add) {
-                                const float4 old = *(const float4*)(dst + j);
-                                r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
-                            }
-                            *(float4*)(dst + j) = r;
+                            for (int j = 0; j < 8; ++j) old[j] = __ldcg((const float4*)(dst + 4 * j));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) old[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float4 r = old[j];
+                            r.x += __uint_as_float(v[4 * j]); r.y += __uint_as_float(v[4 * j + 1]);
+                            r.z += __uint_as_float(v[4 * j + 2]); r.w += __uint_as_float(v[4 * j + 3]);
+                            *(float4*)(dst + 4 * j) = r;
                         }
                     } else {
                         for (int j = 0; j < 32 && n + j < N; ++j)
@@ -273,33 +379,40 @@ static EncodeTiled encode_tiled() {
 }
 
 struct MapKey {
-    const void* base; int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+    const void* base; int rows, cols, box_rows, box_cols, elem_bytes;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows &&
+               box_cols == o.box_cols && elem_bytes == o.elem_bytes;
+    }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.base) ^ ((size_t)k.rows * 0x9E3779B97F4A7C15ull) ^ ((size_t)k.cols << 21) ^ (size_t)k.box_rows;
+        return std::hash<const void*>()(k.base) ^ ((size_t)k.rows * 0x9E3779B97F4A7C15ull) ^ ((size_t)k.cols << 21) ^
+               ((size_t)k.box_rows << 7) ^ ((size_t)k.box_cols << 3) ^ (size_t)k.elem_bytes;
     }
 };
 
-// A row-major [rows, cols] bfloat16 matrix, box of box_rows x 64 elements, 128-byte swizzle.
-static int tensor_map(const void* base, int rows, int cols, int box_rows, CUtensorMap* out) {
+// A row-major [rows, cols] matrix of bfloat16 (elem_bytes 2) or float (4), box of box_rows x box_cols
+// elements whose rows are at most 128 bytes, 128-byte swizzle.
+static int tensor_map(const void* base, int rows, int cols, int elem_bytes, int box_rows, int box_cols,
+                      CUtensorMap* out) {
     static std::mutex lock;
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    const MapKey key{base, rows, cols, box_rows};
+    const MapKey key{base, rows, cols, box_rows, box_cols, elem_bytes};
     std::lock_guard<std::mutex> guard(lock);
     auto found = cache.find(key);
     if (found != cache.end()) { *out = found->second; return 0; }
     EncodeTiled encode = encode_tiled();
     if (!encode) return fail("skv_linear(tcgen05)", "cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * elem_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     CUtensorMap map;
-    const CUresult status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult status = encode(&map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                   2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (status != CUDA_SUCCESS) {
         char detail[64];
         snprintf(detail, sizeof detail, "cuTensorMapEncodeTiled failed with code %d", (int)status);
@@ -314,9 +427,20 @@ static int tensor_map(const void* base, int rows, int cols, int box_rows, CUtens
 template <int BN, int STAGES>
 static int launch_tc(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
                      cudaStream_t stream) {
-    CUtensorMap map_a, map_w;
-    if (int code = tensor_map(a, M, K, TC_BM, &map_a)) return code;
-    if (int code = tensor_map(w, N, K, BN, &map_w)) return code;
+    CUtensorMap map_a, map_w, map_out;
+    if (int code = tensor_map(a, M, K, 2, TC_BM, TC_BK, &map_a)) return code;
+    if (int code = tensor_map(w, N, K, 2, BN, TC_BK, &map_w)) return code;
+    // The epilogue stores through the copy engine when the output's rows are 16-byte multiples;
+    // otherwise (an odd vocabulary, say) the threads store their rows themselves.
+    const bool float_out = mode == TC_MODE_STORE_F32 || mode == TC_MODE_ADD_F32;
+    const int out_cols = mode == TC_MODE_GATED ? N / 2 : N;
+    const int out_elem = float_out ? 4 : 2;
+    int tma_out = ((size_t)out_cols * out_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
+    if (tma_out) {
+        if (int code = tensor_map(out, M, out_cols, out_elem, 32, float_out ? 32 : 64, &map_out)) return code;
+    } else {
+        map_out = map_a;
+    }
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
@@ -327,7 +451,7 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
     }
     dim3 grid((M + TC_BM - 1) / TC_BM, (N + BN - 1) / BN);
     return launch_pdl("skv_linear(tcgen05)", gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(TC_THREADS), smem, stream,
-                      map_a, map_w, out, M, N, K, mode, flag);
+                      map_a, map_w, map_out, tma_out, out, M, N, K, mode, flag);
 }
 
 int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
@@ -335,6 +459,9 @@ int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K,
     if (K % 8 != 0) return fail("skv_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_linear(tcgen05)", "operands must be 16-byte aligned");
     if (mode == TC_MODE_GATED && N % 16 != 0) return fail("skv_linear(tcgen05)", "a gated weight needs a multiple of 16 rows");
+    // Wider tiles re-read less of A and W from L2 per flop; narrow ones waste less on small N.
+    if (N > 128 && (long long)((M + 127) / 128) * ((N + 255) / 256) >= 96)
+        return launch_tc<256, 4>(a, w, out, M, N, K, mode, flag, stream);
     return launch_tc<128, 4>(a, w, out, M, N, K, mode, flag, stream);
 }
 
