@@ -38,6 +38,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// 2^x by the special-function unit; scores are kept in units of log2 (see attention_prefill.cu).
+__device__ __forceinline__ float dec_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *(const uint32_t*)&v;
@@ -69,6 +76,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int my_first = first_group + split * per_split;
     const int my_end = min(end_group, my_first + per_split);
     const int* table = block_table + (size_t)seq * table_width;
+    const float scale_log2 = scale * 1.4426950408889634f;
 
     // Q fragments: rows g and g+8 are heads head0+g and head0+g+8; 4 head-dim elements per k16 step
     uint32_t qa[KSTEPS][4];
@@ -127,7 +135,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int key = j0 + 8 * t + 2 * tig + (c & 1);
-                const float v = (key < ctx && key >= lo) ? s[t][c] * scale : -INFINITY;
+                const float v = (key < ctx && key >= lo) ? s[t][c] * scale_log2 : -INFINITY;
                 s[t][c] = v;
                 tile_max[c >> 1] = fmaxf(tile_max[c >> 1], v);
             }
@@ -140,7 +148,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
             const float new_max = fmaxf(row_max[r], m);
             // a group can be fully masked for this row only through the window's lower edge
-            corr[r] = new_max == -INFINITY ? 1.0f : expf(row_max[r] - new_max);
+            corr[r] = new_max == -INFINITY ? 1.0f : dec_exp2(row_max[r] - new_max);
             row_max[r] = new_max;
         }
         float p[2][4];
@@ -149,7 +157,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float m = row_max[c >> 1];
-                p[t][c] = m == -INFINITY ? 0.0f : expf(s[t][c] - m);
+                p[t][c] = m == -INFINITY ? 0.0f : dec_exp2(s[t][c] - m);
             }
         }
 #pragma unroll
@@ -200,7 +208,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         if (m != -INFINITY) {
             for (int w = 0; w < DEC_WARPS; ++w) {
                 const float* tile = merge + ((size_t)w * 16 + r) * PITCH;
-                const float weight = expf(tile[DHD] - m);          // 0 for a warp that saw no key
+                const float weight = dec_exp2(tile[DHD] - m);      // 0 for a warp that saw no key
                 total += weight * tile[d];
                 sum += weight * tile[DHD + 1];
             }
@@ -230,7 +238,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const
             const size_t at = item * splits + s;
             const float ms = partial_ml[2 * at];
             if (ms == -INFINITY) continue;
-            const float weight = expf(ms - m);
+            const float weight = dec_exp2(ms - m);
             total += weight * partial_o[at * DHD + d];
             sum += weight * partial_ml[2 * at + 1];
         }

@@ -45,6 +45,15 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 
+// 2^x by the special-function unit.  Scores are kept multiplied by log2(e), so that
+// exp(s - m) = 2^(s' - m'); the unit's error (about 2 ulp of float) is far below the
+// bfloat16 rounding the probabilities get before they multiply V.
+__device__ __forceinline__ float pf_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pf_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *(const uint32_t*)&v;
@@ -93,6 +102,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         }
     }
     const int pos_top = ctx_before + row0 + g, pos_bottom = pos_top + 8;   // absolute positions of the two rows
+    const float scale_log2 = scale * 1.4426950408889634f;                  // scores in units of log2
 
     auto load_tile = [&](int kt, int buffer) {
         __nv_bfloat16* k_dst = tiles + (size_t)buffer * 2 * TILE_ELEMS;
@@ -157,7 +167,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                     const int key = kt * PF_BN + 8 * n + 2 * tig + (c & 1);
                     const int pos = (c >> 1) ? pos_bottom : pos_top;
                     const bool seen = key <= pos && (window == 0 || key > pos - window);
-                    const float v = seen ? s[n][c] * scale : -INFINITY;
+                    const float v = seen ? s[n][c] * scale_log2 : -INFINITY;
                     s[n][c] = v;
                     tile_max[c >> 1] = fmaxf(tile_max[c >> 1], v);
                 }
@@ -169,7 +179,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
                 const float new_max = fmaxf(row_max[r], m);
-                corr[r] = new_max == -INFINITY ? 1.0f : expf(row_max[r] - new_max);
+                corr[r] = new_max == -INFINITY ? 1.0f : pf_exp2(row_max[r] - new_max);
                 row_max[r] = new_max;
             }
             float partial[2] = {0.0f, 0.0f};
@@ -178,7 +188,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const float m = row_max[c >> 1];
-                    const float p = m == -INFINITY ? 0.0f : expf(s[n][c] - m);
+                    const float p = m == -INFINITY ? 0.0f : pf_exp2(s[n][c] - m);
                     s[n][c] = p;
                     partial[c >> 1] += p;
                 }

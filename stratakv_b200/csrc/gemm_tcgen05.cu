@@ -126,10 +126,9 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
         : "memory");
 }
 
-__device__ __forceinline__ float silu_gate(float g) {
-    const float sig = g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
-    return g * sig;
-}
+// silu(g) = g / (1 + e^-g), the form of the reference's GPU kernel (src/cuda/gemm_cuda.cu:229).
+// For very negative g the exponential overflows to infinity and the quotient is -0, the right limit.
+__device__ __forceinline__ float silu_gate(float g) { return g / (1.0f + expf(-g)); }
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
