@@ -138,7 +138,7 @@ __device__ __forceinline__ uint4 load_weight16(const uint4* p) {
 // Weights do not depend on the kernel before this one, so the first batch of
 // weight loads is issued before pdl_wait(): it overlaps the predecessor's tail.
 template <int TG, int U, bool STREAM, int MAX_WARPS>
-__global__ void __launch_bounds__(MAX_WARPS * 32)
+__global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS == 4 ? (TG == 1 ? 5 : (TG == 2 ? 4 : 2)) : (MAX_WARPS == 8 && TG <= 2 ? 2 : 1))
 skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                           void* __restrict__ out, int M, int N, int K, int mode, int act) {
     extern __shared__ float red[];                 // [warps][16][8*TG + 1]
@@ -231,23 +231,37 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
 }
 
 template <int TG, int U, int MAX_WARPS>
+static int launch_skinny_as(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+                            int warps, cudaStream_t stream) {
+    const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
+    const size_t smem = (size_t)warps * 16 * (8 * TG + 1) * sizeof(float);
+    dim3 grid(row_tiles, chunks);
+    if (chunks == 1)
+        return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, true, MAX_WARPS>, grid,
+                          dim3(warps * 32), smem, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N,
+                          K, mode, act);
+    return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, false, MAX_WARPS>, grid,
+                      dim3(warps * 32), smem, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K,
+                      mode, act);
+}
+
+// Warps per block.  Many row tiles (>= 4 per SM): 4 warps, compiled to fit 5 blocks on an SM so that
+// e.g. 704 tiles run as one wave.  Few row tiles: 8 warps (two blocks fit on an SM, so the next
+// kernel's weight loads overlap this one's end), or 16 when the inner size is so long that 8 warps
+// would need more than two rounds of loads each.  Never more warps than k steps.
+template <int TG, int U, int MAX_WARPS>
 static int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                          cudaStream_t stream) {
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
     const int steps = (K + 31) / 32;
-    // Few row tiles: many warps per block so that enough loads are in flight on each SM;
-    // many row tiles: several smaller blocks per SM do the same.  Never more warps than k steps.
     const long long blocks = (long long)row_tiles * chunks;
     int warps = blocks >= 148 * 4 ? 4 : 8;
+    if (warps == 8 && MAX_WARPS >= 16 && steps > 8 * U * 2) warps = 16;
     if (warps > MAX_WARPS) warps = MAX_WARPS;
     while (warps > 1 && warps > steps) warps >>= 1;
-    const size_t smem = (size_t)warps * 16 * (8 * TG + 1) * sizeof(float);
-    dim3 grid(row_tiles, chunks);
-    if (chunks == 1)
-        return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, true, MAX_WARPS>, grid, dim3(warps * 32),
-                          smem, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K, mode, act);
-    return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, false, MAX_WARPS>, grid, dim3(warps * 32), smem,
-                      stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K, mode, act);
+    if (warps <= 4) return launch_skinny_as<TG, U, 4>(a, w, out, M, N, K, mode, act, warps, stream);
+    if (warps <= 8 || MAX_WARPS < 16) return launch_skinny_as<TG, U, 8>(a, w, out, M, N, K, mode, act, warps, stream);
+    return launch_skinny_as<TG, U, 16>(a, w, out, M, N, K, mode, act, warps, stream);
 }
 
 // gemm_tcgen05.cu: the tensor-memory GEMM that serves steps with many tokens
@@ -271,8 +285,8 @@ static int launch_linear(const void* a, const void* w, void* out, int M, int N, 
     if (M > 64 && tcgen05_enabled()) return linear_tcgen05(a, w, out, M, N, K, mode, flag, stream);
     // at most 8 warps and under 100 registers a thread: two blocks fit on an SM, so the next
     // kernel's weight loads are in flight while this one finishes
-    if (M <= 8) return launch_skinny<1, 8, 8>(a, w, out, M, N, K, mode, act, stream);
-    if (M <= 16) return launch_skinny<2, 8, 8>(a, w, out, M, N, K, mode, act, stream);
+    if (M <= 8) return launch_skinny<1, 8, 16>(a, w, out, M, N, K, mode, act, stream);
+    if (M <= 16) return launch_skinny<2, 8, 16>(a, w, out, M, N, K, mode, act, stream);
     if (M <= 32) return launch_skinny<4, 4, 8>(a, w, out, M, N, K, mode, act, stream);
     return launch_skinny<8, 4, 8>(a, w, out, M, N, K, mode, act, stream);
 }
