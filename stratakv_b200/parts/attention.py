@@ -36,6 +36,9 @@ class PagedAttention(Mixer):
         if spec.head_dim % 16 != 0:
             raise ValueError(f"attention: head size {spec.head_dim} is not supported "
                              "(the kernels take multiples of 16)")
+        if runtime.dtype == torch.bfloat16 and spec.hidden_size % 8 != 0:
+            raise ValueError(f"attention: hidden size {spec.hidden_size} is not supported in bfloat16 "
+                             "(rows of 16 bytes are needed: a multiple of 8); float32 takes any size")
         self.q_dim = spec.num_heads * spec.head_dim
         self.kv_dim = spec.num_kv_heads * spec.head_dim
         position_spec = spec.position

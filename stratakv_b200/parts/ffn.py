@@ -16,10 +16,15 @@ from .registry import register_ffn
 
 
 def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-    """``[F, H]`` gate and up -> ``[2F, H]`` with rows (gate 8t..8t+7, up 8t..8t+7) per tile ``t``."""
+    """``[F, H]`` gate and up -> ``[2F', H]`` with rows (gate 8t..8t+7, up 8t..8t+7) per tile ``t``.
+    ``F'`` is ``F`` rounded up to a multiple of 8; the added rows are zero (they produce
+    ``act(0) * 0 = 0`` and meet zero columns of the down projection)."""
     rows, cols = gate.shape
     if rows % 8 != 0:
-        raise ValueError(f"gated feed-forward: intermediate size {rows} must be a multiple of 8")
+        pad = 8 - rows % 8
+        gate = torch.cat([gate, gate.new_zeros(pad, cols)])
+        up = torch.cat([up, up.new_zeros(pad, cols)])
+        rows += pad
     tiles = torch.stack([gate.view(rows // 8, 8, cols), up.view(rows // 8, 8, cols)], dim=1)
     return tiles.reshape(2 * rows, cols).contiguous()
 
@@ -31,9 +36,10 @@ class GatedMlp(FeedForward):
         super().__init__(spec, runtime)
         if spec.activation not in _ops.ACTIVATIONS:
             raise ValueError(f"gated feed-forward: activation '{spec.activation}' is not supported")
-        if spec.intermediate_size % 8 != 0:
-            raise ValueError(f"gated feed-forward: intermediate size {spec.intermediate_size} "
-                             "must be a multiple of 8")
+        if runtime.dtype == torch.bfloat16 and spec.hidden_size % 8 != 0:
+            raise ValueError(f"gated feed-forward: hidden size {spec.hidden_size} is not supported in bfloat16 "
+                             "(rows of 16 bytes are needed: a multiple of 8); float32 takes any size")
+        self.padded = -(-spec.intermediate_size // 8) * 8      # the kernels' tiles hold 8 gate and 8 up rows
 
     @classmethod
     def expected_tensors(cls, spec):
@@ -47,12 +53,15 @@ class GatedMlp(FeedForward):
         up = self.rt.upload(tensors[s.up_weight])
         self.w_gate_up = pack_gate_up(gate, up)
         del gate, up
-        self.w_down = self.rt.upload(tensors[s.down_weight])
+        down = self.rt.upload(tensors[s.down_weight])
+        if self.padded != s.intermediate_size:
+            down = torch.cat([down, down.new_zeros(down.shape[0], self.padded - s.intermediate_size)], dim=1)
+        self.w_down = down.contiguous()
 
     def forward(self, step, h, x):
         s, rt = self.spec, self.rt
         ops = rt.kernels()
-        z = rt.workspace.get("ffn_hidden", (h.shape[0], s.intermediate_size), rt.dtype)
+        z = rt.workspace.get("ffn_hidden", (h.shape[0], self.padded), rt.dtype)
         ops.linear(h, self.w_gate_up, z, _ops.MODE_GATED, s.activation)
         ops.linear(z, self.w_down, x, _ops.MODE_ADD_F32)
 

@@ -25,7 +25,12 @@ TINY_C = dict(architectures=["LlamaForCausalLM"], hidden_size=80, intermediate_s
               num_hidden_layers=1, num_attention_heads=3, num_key_value_heads=3, head_dim=32,
               vocab_size=331, rms_norm_eps=3e-6, rope_theta=25000.0, max_position_embeddings=512,
               tie_word_embeddings=False, hidden_act="silu")
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Awkward sizes: a feed-forward width that is no multiple of 8, seven query heads on one KV head.
+TINY_D = dict(architectures=["LlamaForCausalLM"], hidden_size=56, intermediate_size=90,
+              num_hidden_layers=2, num_attention_heads=7, num_key_value_heads=1, head_dim=16,
+              vocab_size=203, rms_norm_eps=1e-5, rope_theta=1000.0, max_position_embeddings=256,
+              tie_word_embeddings=True, hidden_act="silu")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_folder(folder, raw_config, seed, dtype=torch.float32):

@@ -134,3 +134,29 @@ def test_padding_and_company_change_nothing(folders, dtype):
     torch.testing.assert_close(together, alone, rtol=rtol, atol=atol)
     for s in slots:
         engine.close_sequence(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batches_that_do_not_fill_a_graph_bucket(folders, plain, dtype):
+    """Nine, then five, then eleven sequences decode together: the decode graph pads its batch up to
+    a bucket, and the padding rows (which read and write a spare cache block) must change nothing."""
+    from stratakv_b200 import StepEntry
+    name = "B"
+    engine = engine_for(folders[name], dtype, max_tokens=64 * 24)
+    vocab = TINY[name]["vocab_size"]
+    for batch in (9, 5, 11):
+        requests = []
+        for i in range(batch):
+            tokens = random_tokens(vocab, 3 + 5 * i + 6, seed=1000 + batch * 31 + i)
+            requests.append(dict(tokens=tokens, prompt=3 + 5 * i, slot=engine.open_sequence(), ref=plain(name, tokens)))
+        got = engine.step([StepEntry(r["slot"], r["tokens"][:r["prompt"]], [r["prompt"] - 1]) for r in requests])
+        check(got, np.stack([r["ref"][r["prompt"] - 1] for r in requests]), dtype, f"prompts of batch {batch}")
+        for step in range(6):
+            wanted = [r for i, r in enumerate(requests) if (i + step) % 3 != 0]      # some rows want no logits
+            entries = [StepEntry(r["slot"], [r["tokens"][r["prompt"] + step]], [0] if r in wanted else [])
+                       for r in requests]
+            got = engine.step(entries)
+            check(got, np.stack([r["ref"][r["prompt"] + step] for r in wanted]), dtype, f"batch {batch} step {step}")
+        for r in requests:
+            engine.close_sequence(r["slot"])
+        assert engine.cache.all_free()
