@@ -183,6 +183,27 @@ class Kernels:
             _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), n, num_heads, num_kv_heads, head_dim, block_size,
             ctypes.c_float(scale), window, splits, _stream()), "attention_decode")
 
+    def attention_decode_fused(self, qkv, cos_sin, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
+                               num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
+                               splits: int = 1, write_kv: bool = True):
+        """One new token per sequence (bfloat16 build), from the float32 q|k|v projection: rotates queries
+        and the new key (``cos_sin`` table, or ``None`` for no rotation), writes the new key and value into
+        the cache, attends over ``ctx_after[s]`` keys and merges ``splits`` (1..8) context pieces in-kernel."""
+        self._want(qkv, torch.float32, "qkv"); self._want(out, self.dtype, "out")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
+        self._want(block_table, torch.int32, "block_table"); self._want(ctx_after, torch.int32, "ctx_after")
+        if cos_sin is not None:
+            self._want(cos_sin, torch.float32, "cos_sin")
+        n = qkv.shape[0]
+        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+            raise KernelError("attention_decode_fused: qkv width does not match the head counts")
+        if ctx_after.numel() != n or block_table.shape[0] != n:
+            raise KernelError("attention_decode_fused: one length and one table row per sequence is needed")
+        self._check(self.lib.skv_attention_decode_fused(
+            _ptr(qkv), _ptr(cos_sin), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+            _ptr(ctx_after), _ptr(out), n, num_heads, num_kv_heads, head_dim, block_size, ctypes.c_float(scale),
+            window, splits, int(bool(write_kv)), _stream()), "attention_decode_fused")
+
     def add_inplace(self, out, other):
         self._want(out, torch.float32, "out"); self._want(other, torch.float32, "other")
         if out.numel() != other.numel():

@@ -73,12 +73,21 @@ class PagedAttention(Mixer):
         ops.linear(h, self.w_qkv, qkv, _ops.MODE_STORE_F32)
         k_cache, v_cache = step.cache.entry_kv(cache_entry)
         table = step.block_tables[step.cache.entry_group_index(cache_entry)]
+        ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
+        blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
+        if step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table"):
+            # one kernel: rotation, cache write, attention over the context in up to 8 pieces, merge
+            splits = min(8, decode_splits(n, blocks_per_seq, step.max_ctx))
+            ops.attention_decode_fused(qkv, self.position.fusion_table(step.max_ctx), k_cache, v_cache, table,
+                                       step.ctx_after, ctx, s.num_heads, s.num_kv_heads, s.head_dim,
+                                       step.cache.block_size, s.scale, s.window, splits, writes_cache)
+            ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32)
+            return
         q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
         self.position.rotate_and_store(step, qkv, q, k_cache, v_cache, table, s.num_heads, s.num_kv_heads,
                                        s.head_dim, step.cache.block_size, writes_cache)
-        ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
         if step.is_decode and rt.dtype == torch.bfloat16:
-            splits = decode_splits(n, s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16)), step.max_ctx)
+            splits = decode_splits(n, blocks_per_seq, step.max_ctx)
             scratch_o = scratch_ml = None
             if splits > 1:
                 scratch_o = rt.workspace.get("attn_split_o", (n * s.num_heads * splits * s.head_dim,), torch.float32)

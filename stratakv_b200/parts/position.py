@@ -45,6 +45,11 @@ class RopeHalf:
         self.table = host.to(self.rt.device).contiguous()
         self.length = length
 
+    def fusion_table(self, max_positions: int):
+        """The (cos, sin) table for kernels that rotate queries and keys themselves."""
+        self.ensure(max_positions)
+        return self.table
+
     def rotate_and_store(self, step, qkv, q_out, k_cache, v_cache, block_table, num_heads, num_kv_heads,
                          head_dim, block_size, write_kv):
         if head_dim != self.spec.head_dim:
@@ -65,6 +70,9 @@ class NoPosition:
 
     def ensure(self, positions: int) -> None:
         pass
+
+    def fusion_table(self, max_positions: int):
+        return None
 
     def rotate_and_store(self, step, qkv, q_out, k_cache, v_cache, block_table, num_heads, num_kv_heads,
                          head_dim, block_size, write_kv):

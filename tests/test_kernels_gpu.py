@@ -377,3 +377,53 @@ def test_attention_prefill_at_the_edges_of_tiles_and_windows():
         got = out[query, head_dim:].float().cpu()
         want = setup["values"][0][far, 0].to(dtype).float()
         assert torch.allclose(got, want, rtol=2e-2, atol=2e-2) == visible
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size,lengths,window,splits,rotate", [
+    (4, 2, 16, 16, [5, 40, 17, 1], 0, 1, True),
+    (6, 3, 48, 16, [33, 1, 100], 0, 3, True),
+    (32, 4, 64, 64, [700, 129, 2048, 64, 65], 0, 8, True),
+    (8, 8, 128, 32, [300, 31], 0, 2, True),
+    (20, 1, 32, 16, [90, 45], 0, 4, True),                 # more than 16 query heads on one KV head
+    (4, 2, 32, 16, [90, 45, 7], 20, 2, True),              # a window
+    (8, 2, 80, 64, [500, 16, 17], 0, 8, False),            # no rotation; more splits than work for some
+])
+def test_attention_decode_fused_equals_the_separate_kernels(heads, kv_heads, head_dim, block_size, lengths, window,
+                                                            splits, rotate):
+    """Rotation + cache write + split attention + merge in one kernel, against rope_kv_write followed by
+    attention_decode; the cache must hold the same new rows afterwards and nothing else may change."""
+    from stratakv_b200.parts.position import rope_table
+    dtype = torch.bfloat16
+    k = lib(dtype, head_dim)
+    n = len(lengths)
+    setup = paged_setup(dtype, lengths, [1] * n, heads, kv_heads, head_dim, block_size, seed=heads * 7 + head_dim)
+    g = torch.Generator().manual_seed(99)
+    qkv = torch.randn(n, (heads + 2 * kv_heads) * head_dim, generator=g).cuda()
+    table = torch.from_numpy(rope_table(head_dim, 5000.0, 2048)).cuda() if rotate else None
+    ctx_after = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    scale = 0.5 / math.sqrt(head_dim)
+    # the separate kernels
+    k1, v1 = setup["k_cache"].clone(), setup["v_cache"].clone()
+    q = torch.zeros(n, heads * head_dim, device="cuda").to(dtype)
+    k.rope_kv_write(qkv, table, setup["positions"], setup["token_seq"], setup["table"], q, k1, v1, heads, kv_heads,
+                    head_dim, block_size, True)
+    expected = torch.zeros_like(q)
+    so = torch.zeros(n * heads * 8 * head_dim, device="cuda")
+    sm = torch.zeros(n * heads * 8 * 2, device="cuda")
+    k.attention_decode(q, k1, v1, setup["table"], ctx_after, expected, heads, kv_heads, head_dim, block_size, scale,
+                       window, splits, so, sm)
+    # the fused kernel
+    k2, v2 = setup["k_cache"].clone(), setup["v_cache"].clone()
+    got = torch.full_like(q, float("nan"))
+    k.attention_decode_fused(qkv, table, k2, v2, setup["table"], ctx_after, got, heads, kv_heads, head_dim, block_size,
+                             scale, window, splits, True)
+    torch.cuda.synchronize()
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    torch.testing.assert_close(got.float(), expected.float(), rtol=1.6e-2, atol=1e-2)
+    # reading only: the cache stays as it was, and the result is the same over the rows already there
+    k3, v3 = k1.clone(), v1.clone()
+    again = torch.full_like(q, float("nan"))
+    k.attention_decode_fused(qkv, table, k3, v3, setup["table"], ctx_after, again, heads, kv_heads, head_dim,
+                             block_size, scale, window, splits, False)
+    assert torch.equal(k3, k1) and torch.equal(v3, v1)
+    torch.testing.assert_close(again.float(), expected.float(), rtol=1.6e-2, atol=1e-2)
