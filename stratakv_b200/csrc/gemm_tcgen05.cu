@@ -2,15 +2,17 @@
 // float accumulation in tensor memory, fused epilogue (the modes of linear.cu).
 //
 // This is what replaces the reference's 32x32 shared-memory tile GEMM
-// (src/cuda/gemm_cuda.cu:445-525) when a step brings many tokens.  One block computes a
-// 128 x BN tile of the output:
+// (src/cuda/gemm_cuda.cu:445-525) when a step brings many tokens.  At most one block per SM runs; it
+// walks over 128 x BN tiles of the output with two accumulators in tensor memory, so that the epilogue
+// of one tile overlaps the main loop of the next:
 //   warp 0   one thread issues TMA loads (cp.async.bulk.tensor) of 128x64 A and BNx64 W tiles
 //            into a ring of shared-memory stages, 128-byte swizzled, completing on mbarriers;
-//   warp 1   allocates BN columns of tensor memory; one thread issues tcgen05.mma
+//   warp 1   allocates 2 x BN columns of tensor memory; one thread issues tcgen05.mma
 //            (128 x BN x 16 per instruction, four per stage) and commits each stage back to
 //            the loader, and the finished accumulator to the epilogue;
 //   warps 2-5 read the accumulator with tcgen05.ld (each warp its quarter of the 128 lanes,
-//            one output row per thread) and apply the epilogue.
+//            one output row per thread), apply the epilogue into swizzled slabs of shared memory and
+//            send them out with TMA stores (reduce-add for the residual).
 // Tails in M, N and K are zero-filled by TMA and masked in the epilogue.
 //
 // Every wait on an mbarrier gives up after a bounded number of tries, raises bit 2 (value 4)
@@ -130,31 +132,186 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
 // For very negative g the exponential overflows to infinity and the quotient is -0, the right limit.
 __device__ __forceinline__ float silu_gate(float g) { return g / (1.0f + expf(-g)); }
 
+// The epilogue of one output tile for one of the four epilogue warps: reads the warp's quarter of the
+// accumulator (TMEM lanes 32*quarter .., one output row per thread) and stores it in the mode asked for.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, int lane, uint8_t* slabs, int& buffer,
+                                              const CUtensorMap* map_out, int tma_out, void* __restrict__ out, int M,
+                                              int N, int mode, int m0, int n0) {
+    const int m = m0 + quarter * 32 + lane;
+    if (tma_out) {
+        // Each thread builds 128 bytes of its output row in a swizzled slab of shared memory; one lane
+        // hands the warp's 32 x 128-byte slab to the copy engine, which writes whole rows (or adds them,
+        // for the residual) and clips at M and N.
+        // Two slabs per warp alternate so that one is written while the other is being read.
+        const uint32_t lane_base = acc_tmem + ((uint32_t)(quarter * 32) << 16);
+        const int y = m0 + quarter * 32;
+        // accumulator columns that make one 128-byte output row, and output columns per slab
+        const int acc_per_slab = mode == TC_MODE_GATED ? 128 : (mode == TC_MODE_STORE ? 64 : 32);
+        const int out_per_slab = mode == TC_MODE_STORE_F32 || mode == TC_MODE_ADD_F32 ? 32 : 64;
+        const int out_x0 = mode == TC_MODE_GATED ? (n0 >> 1) : n0;
+#pragma unroll 1
+        for (int seg = 0; seg * acc_per_slab < BN; ++seg) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            uint8_t* slab = slabs + buffer * 4096;
+#pragma unroll 1
+            for (int sub = 0; sub * 32 < acc_per_slab; ++sub) {
+                uint32_t v[32];
+                tmem_load_32(lane_base + (uint32_t)(seg * acc_per_slab + sub * 32), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (mode == TC_MODE_GATED) {
+                    // 32 accumulator columns = two groups of (8 gate, 8 up) -> 16 outputs = 2 pieces
+#pragma unroll
+                    for (int grp = 0; grp < 2; ++grp) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float lo = silu_gate(__uint_as_float(v[16 * grp + 2 * j])) *
+                                             __uint_as_float(v[16 * grp + 8 + 2 * j]);
+                            const float hi = silu_gate(__uint_as_float(v[16 * grp + 2 * j + 1])) *
+                                             __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+                            packed[j] = *(const uint32_t*)&pair;
+                        }
+                        slab_write(slab, lane, sub * 2 + grp, make_uint4(packed[0], packed[1], packed[2], packed[3]));
+                    }
+                } else if (mode == TC_MODE_STORE) {
+#pragma unroll
+                    for (int piece = 0; piece < 4; ++piece) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(
+                                __uint_as_float(v[8 * piece + 2 * e]), __uint_as_float(v[8 * piece + 2 * e + 1]));
+                            packed[e] = *(const uint32_t*)&pair;
+                        }
+                        slab_write(slab, lane, sub * 4 + piece, make_uint4(packed[0], packed[1], packed[2], packed[3]));
+                    }
+                } else {
+#pragma unroll
+                    for (int piece = 0; piece < 8; ++piece)
+                        slab_write(slab, lane, piece, make_uint4(v[4 * piece], v[4 * piece + 1], v[4 * piece + 2], v[4 * piece + 3]));
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                const int x = out_x0 + seg * out_per_slab;
+                const int out_cols = mode == TC_MODE_GATED ? (N >> 1) : N;
+                if (x < out_cols && y < M) {             // a slab wholly outside the matrix is not sent
+                    if (mode == TC_MODE_ADD_F32) tma_reduce_add_2d(map_out, x, y, smem_addr(slab));
+                    else tma_store_2d(map_out, x, y, smem_addr(slab));
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            buffer ^= 1;
+        }
+    } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+            uint32_t v[32];
+            tmem_load_32(acc_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (m >= M) continue;
+            const int n = n0 + c;
+            if (mode == TC_MODE_GATED) {
+                // columns come in groups of 16: 8 gate columns, then their 8 up columns
+                const int half_n = N >> 1;
+                __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)m * half_n + (n >> 1);
+#pragma unroll
+                for (int grp = 0; grp < 2; ++grp) {
+                    if (n + 16 * grp < N) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float lo = silu_gate(__uint_as_float(v[16 * grp + 2 * j])) *
+                                             __uint_as_float(v[16 * grp + 8 + 2 * j]);
+                            const float hi = silu_gate(__uint_as_float(v[16 * grp + 2 * j + 1])) *
+                                             __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+                            packed[j] = *(const uint32_t*)&pair;
+                        }
+                        *(uint4*)(dst + 8 * grp) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                }
+            } else if (mode == TC_MODE_STORE) {
+                __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)m * N + n;
+                if (n + 32 <= N && (N & 7) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]),
+                                                                              __uint_as_float(v[j + 2 * e + 1]));
+                            packed[e] = *(const uint32_t*)&pair;
+                        }
+                        *(uint4*)(dst + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                } else {
+                    for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                }
+            } else {
+                float* dst = (float*)out + (size_t)m * N + n;
+                const bool add = mode == TC_MODE_ADD_F32;
+                if (n + 32 <= N && (N & 3) == 0) {
+                    // all old values are fetched before anything is stored: a store between two
+                    // loads of the same array would make each load wait for the one before
+                    float4 old[8];
+                    if (add) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) old[j] = __ldcg((const float4*)(dst + 4 * j));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) old[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 r = old[j];
+                        r.x += __uint_as_float(v[4 * j]); r.y += __uint_as_float(v[4 * j + 1]);
+                        r.z += __uint_as_float(v[4 * j + 2]); r.w += __uint_as_float(v[4 * j + 3]);
+                        *(float4*)(dst + 4 * j) = r;
+                    }
+                } else {
+                    for (int j = 0; j < 32 && n + j < N; ++j)
+                        dst[j] = (add ? dst[j] : 0.0f) + __uint_as_float(v[j]);
+                }
+            }
+        }
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
                     int N, int K, int mode, int* __restrict__ flag) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    constexpr uint32_t SLAB_BYTES = 4 * 2 * 4096;           // four epilogue warps, two 32 x 128-byte slabs each
     extern __shared__ uint8_t smem_raw[];
-    // tiles need 1024-byte alignment for the 128-byte swizzle
+    // tiles and slabs need 1024-byte alignment for the 128-byte swizzle
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(tiles + (size_t)STAGES * STAGE_BYTES);     // full[STAGES], empty[STAGES], accum
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    uint8_t* slab_base = tiles + (size_t)STAGES * STAGE_BYTES;
+    uint64_t* bars = (uint64_t*)(slab_base + SLAB_BYTES);   // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
     const int k_iters = (K + TC_BK - 1) / TC_BK;
-    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES), accum = smem_addr(bars + 2 * STAGES);
+    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
+    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
+    const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(accum, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
+        // two accumulators of BN columns each: the epilogue of one tile overlaps the main loop of the next
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)BN) : "memory");
+                     ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -163,200 +320,86 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();                                   // A is the previous kernel's output
 
+    // A block walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...; neighbouring tiles share their
+    // W rows (m runs fastest), so blocks that run together read the same W tile from L2.
     if (warp == 0 && lane == 0) {
         // ---- loader -------------------------------------------------------------------------
         bool ok = true;
-        int armed = 0;
-        for (int i = 0; i < k_iters && ok; ++i) {
-            const int s = i % STAGES;
-            if (i >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, flag);
-            if (!ok) break;
-            const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            tma_load_2d(a_dst, &map_a, i * TC_BK, m0, full0 + 8 * s);
-            tma_load_2d(a_dst + A_BYTES, &map_w, i * TC_BK, n0, full0 + 8 * s);
-            armed = i + 1;
+        int it = 0;                               // k iterations issued so far, over all tiles
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            for (int i = 0; i < k_iters; ++i, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, flag);
+                if (!ok) break;
+                const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, i * TC_BK, m0, full0 + 8 * s);
+                tma_load_2d(a_dst + A_BYTES, &map_w, i * TC_BK, n0, full0 + 8 * s);
+            }
         }
         if (!ok) {
             // let the copies in flight land before the block leaves (bounded)
-            for (int i = max(0, armed - STAGES); i < armed; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr);
+            for (int i = max(0, it - STAGES); i < it; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- tensor-core issue ------------------------------------------------------------------
         constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
         bool ok = true;
-        for (int i = 0; i < k_iters && ok; ++i) {
-            const int s = i % STAGES;
-            ok = mbar_wait(full0 + 8 * s, (i / STAGES) & 1, flag);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-            const uint64_t a_desc = umma_desc(a_addr), w_desc = umma_desc(a_addr + A_BYTES);
-#pragma unroll
-            for (int k = 0; k < TC_BK / 16; ++k) {
-                // 16 bfloat16 = 32 bytes further along K: +2 in the descriptor's 16-byte units
-                umma_bf16(tmem_base, a_desc + 2 * k, w_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        int it = 0, local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            if (local >= 2) {                     // the epilogue must have drained this accumulator
+                ok = mbar_wait(acc_empty0 + 8 * buf, ((local >> 1) - 1) & 1, flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            umma_commit(empty0 + 8 * s);          // frees the stage when these MMAs have read it
+            const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+            for (int i = 0; i < k_iters; ++i, ++it) {
+                const int s = it % STAGES;
+                ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                const uint64_t a_desc = umma_desc(a_addr), w_desc = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k) {
+                    // 16 bfloat16 = 32 bytes further along K: +2 in the descriptor's 16-byte units
+                    umma_bf16(acc, a_desc + 2 * k, w_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(empty0 + 8 * s);      // frees the stage when these MMAs have read it
+            }
+            if (ok) umma_commit(acc_full0 + 8 * buf);   // arrives when every MMA of the tile has finished
         }
-        umma_commit(accum);                       // arrives when every MMA above has finished
     } else if (warp >= 2) {
         // ---- epilogue ---------------------------------------------------------------------------
-        const bool ok = mbar_wait(accum, 0, flag);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quarter = warp & 3;             // the TMEM lanes this warp may read
-        const int m = m0 + quarter * 32 + lane;
-        if (ok && tma_out) {
-            // Each thread builds 128 bytes of its output row in a swizzled slab of shared memory (the
-            // pipeline's first stage is free by now); one lane hands the warp's 32 x 128-byte slab to the
-            // copy engine, which writes whole rows (or adds them, for the residual) and clips at M and N.
-            // Two slabs per warp alternate so that one is written while the other is being read.
-            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            uint8_t* slabs = tiles + quarter * 8192;
-            const int y = m0 + quarter * 32;
-            // accumulator columns that make one 128-byte output row, and output columns per slab
-            const int acc_per_slab = mode == TC_MODE_GATED ? 128 : (mode == TC_MODE_STORE ? 64 : 32);
-            const int out_per_slab = mode == TC_MODE_STORE_F32 || mode == TC_MODE_ADD_F32 ? 32 : 64;
-            const int out_x0 = mode == TC_MODE_GATED ? (n0 >> 1) : n0;
-            int buffer = 0;
-#pragma unroll 1
-            for (int seg = 0; seg * acc_per_slab < BN; ++seg) {
-                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                __syncwarp();
-                uint8_t* slab = slabs + buffer * 4096;
-#pragma unroll 1
-                for (int sub = 0; sub * 32 < acc_per_slab; ++sub) {
-                    uint32_t v[32];
-                    tmem_load_32(lane_base + (uint32_t)(seg * acc_per_slab + sub * 32), v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (mode == TC_MODE_GATED) {
-                        // 32 accumulator columns = two groups of (8 gate, 8 up) -> 16 outputs = 2 pieces
-#pragma unroll
-                        for (int grp = 0; grp < 2; ++grp) {
-                            uint32_t packed[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const float lo = silu_gate(__uint_as_float(v[16 * grp + 2 * j])) *
-                                                 __uint_as_float(v[16 * grp + 8 + 2 * j]);
-                                const float hi = silu_gate(__uint_as_float(v[16 * grp + 2 * j + 1])) *
-                                                 __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
-                                const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
-                                packed[j] = *(const uint32_t*)&pair;
-                            }
-                            slab_write(slab, lane, sub * 2 + grp, make_uint4(packed[0], packed[1], packed[2], packed[3]));
-                        }
-                    } else if (mode == TC_MODE_STORE) {
-#pragma unroll
-                        for (int piece = 0; piece < 4; ++piece) {
-                            uint32_t packed[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const __nv_bfloat162 pair = __floats2bfloat162_rn(
-                                    __uint_as_float(v[8 * piece + 2 * e]), __uint_as_float(v[8 * piece + 2 * e + 1]));
-                                packed[e] = *(const uint32_t*)&pair;
-                            }
-                            slab_write(slab, lane, sub * 4 + piece, make_uint4(packed[0], packed[1], packed[2], packed[3]));
-                        }
-                    } else {
-#pragma unroll
-                        for (int piece = 0; piece < 8; ++piece)
-                            slab_write(slab, lane, piece, make_uint4(v[4 * piece], v[4 * piece + 1], v[4 * piece + 2], v[4 * piece + 3]));
-                    }
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) {
-                    const int x = out_x0 + seg * out_per_slab;
-                    const int out_cols = mode == TC_MODE_GATED ? (N >> 1) : N;
-                    if (x < out_cols && y < M) {             // a slab wholly outside the matrix is not sent
-                        if (mode == TC_MODE_ADD_F32) tma_reduce_add_2d(&map_out, x, y, smem_addr(slab));
-                        else tma_store_2d(&map_out, x, y, smem_addr(slab));
-                    }
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                }
-                buffer ^= 1;
-            }
+        uint8_t* slabs = slab_base + quarter * 8192;
+        int buffer = 0, local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            epilogue_tile<BN>(tmem_base + (uint32_t)(buf * BN), quarter, lane, slabs, buffer, &map_out, tma_out, out, M, N,
+                              mode, m0, n0);
+            // the accumulator has been read out: hand it back to the issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
+        }
+        if (tma_out) {
             if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
             __syncwarp();
-        } else if (ok) {
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                tmem_load_32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (m >= M) continue;
-                const int n = n0 + c;
-                if (mode == TC_MODE_GATED) {
-                    // columns come in groups of 16: 8 gate columns, then their 8 up columns
-                    const int half_n = N >> 1;
-                    __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)m * half_n + (n >> 1);
-#pragma unroll
-                    for (int grp = 0; grp < 2; ++grp) {
-                        if (n + 16 * grp < N) {
-                            uint32_t packed[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const float lo = silu_gate(__uint_as_float(v[16 * grp + 2 * j])) *
-                                                 __uint_as_float(v[16 * grp + 8 + 2 * j]);
-                                const float hi = silu_gate(__uint_as_float(v[16 * grp + 2 * j + 1])) *
-                                                 __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
-                                const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
-                                packed[j] = *(const uint32_t*)&pair;
-                            }
-                            *(uint4*)(dst + 8 * grp) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        }
-                    }
-                } else if (mode == TC_MODE_STORE) {
-                    __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)m * N + n;
-                    if (n + 32 <= N && (N & 7) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint32_t packed[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]),
-                                                                                  __uint_as_float(v[j + 2 * e + 1]));
-                                packed[e] = *(const uint32_t*)&pair;
-                            }
-                            *(uint4*)(dst + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
-                    }
-                } else {
-                    float* dst = (float*)out + (size_t)m * N + n;
-                    const bool add = mode == TC_MODE_ADD_F32;
-                    if (n + 32 <= N && (N & 3) == 0) {
-                        // all old values are fetched before anything is stored: a store between two
-                        // loads of the same array would make each load wait for the one before
-                        float4 old[8];
-                        if (add) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) old[j] = __ldcg((const float4*)(dst + 4 * j));
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) old[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float4 r = old[j];
-                            r.x += __uint_as_float(v[4 * j]); r.y += __uint_as_float(v[4 * j + 1]);
-                            r.z += __uint_as_float(v[4 * j + 2]); r.w += __uint_as_float(v[4 * j + 3]);
-                            *(float4*)(dst + 4 * j) = r;
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && n + j < N; ++j)
-                            dst[j] = (add ? dst[j] : 0.0f) + __uint_as_float(v[j]);
-                    }
-                }
-            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
     }
 }
 
@@ -440,7 +483,8 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
     } else {
         map_out = map_a;
     }
-    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 4 * 2 * 4096 +
+                            (2 * STAGES + 4) * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
         const cudaError_t status = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>,
@@ -448,7 +492,15 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
         if (status != cudaSuccess) return fail("skv_linear(tcgen05)", cudaGetErrorString(status));
         configured = true;
     }
-    dim3 grid((M + TC_BM - 1) / TC_BM, (N + BN - 1) / BN);
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0)
+            return fail("skv_linear(tcgen05)", "cannot read the number of SMs");
+    }
+    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));     // one persistent block per SM at most
     return launch_pdl("skv_linear(tcgen05)", gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(TC_THREADS), smem, stream,
                       map_a, map_w, map_out, tma_out, out, M, N, K, mode, flag);
 }
