@@ -120,6 +120,10 @@ class Model:
     def forward(self, step: StepBatch, want_rows: Optional[torch.Tensor], n_want: int):
         """Run the step's tokens; return float32 logits ``[n_want, vocab]`` (a view
         of scratch memory that the next step overwrites) or ``None``."""
+        with _ops.stream_scope():
+            return self._forward(step, want_rows, n_want)
+
+    def _forward(self, step: StepBatch, want_rows: Optional[torch.Tensor], n_want: int):
         rt, spec = self.rt, self.spec
         ops = rt.kernels()
         x = rt.workspace.get("residual", (step.n_tokens, spec.hidden_size), torch.float32)

@@ -26,8 +26,30 @@ def _ptr(tensor: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
 
 
+_SCOPED_STREAM = None
+
+
 def _stream():
+    if _SCOPED_STREAM is not None:
+        return _SCOPED_STREAM
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_scope:
+    """Within the scope every kernel goes to the stream that was current when the scope began
+    (asking torch for the current stream at each of a step's two hundred launches costs more
+    than the launches themselves)."""
+
+    def __enter__(self):
+        global _SCOPED_STREAM
+        self.previous = _SCOPED_STREAM
+        _SCOPED_STREAM = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream) if torch.cuda.is_available() else None
+        return self
+
+    def __exit__(self, *exc):
+        global _SCOPED_STREAM
+        _SCOPED_STREAM = self.previous
+        return False
 
 
 class Kernels:
