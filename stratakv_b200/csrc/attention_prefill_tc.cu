@@ -1,0 +1,437 @@
+// Prefill attention on the 5th-generation tensor cores (bfloat16, head size 64 or 128): causal
+// grouped-query flash attention over the paged cache with both matrix products in tcgen05.mma.
+//
+// It does the arithmetic of attention_prefill.cu (src/layers/attention.cpp:261-338 in the
+// reference, which has no prefill kernel at all) with another division of labour.  A block takes
+// 128 queries of one head; keys and values come in tiles of 128 positions:
+//   warp 0   one thread: TMA loads of the Q tile (once) and of K and V tiles into two-stage rings;
+//            a tile is gathered from the cache blocks the sequence's block table names;
+//   warp 1   one thread: S = Q.K^T (128 x 128 x head_dim) into the score buffer in tensor memory,
+//            and O_j = P.V (128 x head_dim x 128) into the output buffer;
+//            V is used as it lies in the cache (positions x head_dim), as an MN-major operand;
+//   warps 2-5  one thread per query row: read the scores with tcgen05.ld, mask, running maximum,
+//            2^x on the special-function unit (scores carry log2 e), row sums, probabilities as
+//            bfloat16 into a swizzled shared-memory tile (the A operand of P.V), and the running
+//            output in registers: O = O * 2^(m_old - m_new) + O_j, read back from tensor memory.
+// The softmax is the long pole (one warp per scheduler runs its dependent chains at a fraction of the
+// issue rate), so a block uses only half of the SM's tensor memory and shared memory and two blocks
+// share an SM: while one block's rows are in the softmax the other's products run.  Every mbarrier
+// wait is bounded; on time-out bit 2 (value 4) of the flag word is raised and the block drains.
+#include "common.cuh"
+
+#if SKV_DTYPE == SKV_BF16 && (SKV_HEAD_DIM == 64 || SKV_HEAD_DIM == 128)
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <utility>
+#include <vector>
+
+namespace skv {
+
+constexpr int AHD = SKV_HEAD_DIM;
+constexpr int ACH = AHD / 64;                       // 64-wide (128-byte) chunks of a head
+constexpr int ABM = 128, ABN = 128;                 // queries and keys per tile
+constexpr int ATHREADS = 192;
+constexpr uint32_t AWAIT = 1u << 20;
+constexpr uint32_t TILE_BYTES = 128 * 128;          // one 128-row x 128-byte swizzled tile
+
+__device__ __forceinline__ uint32_t a_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void a_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void a_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void a_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool a_wait(uint32_t bar, uint32_t parity, int* flag) {
+    for (uint32_t tries = 0; tries < AWAIT; ++tries) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    if (flag) atomicOr(flag, 4);
+    return false;
+}
+__device__ __forceinline__ void a_tma(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// 128-byte-swizzled tile with 128-byte rows; 1024 bytes between groups of 8 rows (see gemm_tcgen05.cu)
+__device__ __forceinline__ uint64_t a_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16, float accumulator, bfloat16 operands; b_mn = 1: B is MN-major (rows are the K index)
+__device__ __forceinline__ constexpr uint32_t a_idesc(int m, int n, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void a_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void a_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void a_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ float a_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PE = 14, B_OF = 15,
+       B_OE = 17, B_COUNT = 19 };
+
+__global__ void __launch_bounds__(ATHREADS, 2)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
+                            int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_after,
+                            __nv_bfloat16* __restrict__ out, int num_heads, int num_kv_heads, int block_size,
+                            int rows_per_load, float scale, int window, int tiles_per_seq, int* __restrict__ flag) {
+    extern __shared__ uint8_t a_raw[];
+    uint8_t* base = (uint8_t*)(((uintptr_t)a_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_tile = base;                                        // ACH tiles
+    uint8_t* k_ring = q_tile + ACH * TILE_BYTES;                   // 2 stages x ACH tiles
+    uint8_t* v_ring = k_ring + 2 * ACH * TILE_BYTES;               // 1 stage x ACH tiles
+    uint8_t* p_tile = v_ring + ACH * TILE_BYTES;                   // 2 tiles (keys 0-63, 64-127)
+    uint64_t* bars = (uint64_t*)(p_tile + 2 * TILE_BYTES);
+    uint32_t* tmem_slot = (uint32_t*)(bars + B_COUNT);
+    const uint32_t bar0 = a_smem(bars);
+    auto bar = [&](int which, int index = 0) { return bar0 + 8u * (uint32_t)(which + index); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.x / tiles_per_seq, tile = blockIdx.x - seq * tiles_per_seq;
+    const int head = blockIdx.y;
+    const int kv_head = head / (num_heads / num_kv_heads);
+    pdl_launch_dependents();
+    const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
+    if (tile * ABM >= q_len) return;                               // the whole block leaves together
+    const int ctx = ctx_after[seq], ctx_before = ctx - q_len;
+    const int last_query = min(q_len, tile * ABM + ABM) - 1;
+    const int kv_end = ctx_before + last_query + 1;
+    const int kv_lo = window > 0 ? max(0, ctx_before + tile * ABM - window + 1) : 0;
+    const int first_tile = kv_lo / ABN, n_tiles = (kv_end + ABN - 1) / ABN - first_tile;
+
+    if (threadIdx.x == 0) {
+        a_init(bar(B_Q), 1);
+        for (int i = 0; i < 2; ++i) {
+            a_init(bar(B_KF, i), 1); a_init(bar(B_KE, i), 1); a_init(bar(B_VF, i), 1); a_init(bar(B_VE, i), 1);
+            a_init(bar(B_SF, i), 1); a_init(bar(B_SE, i), 4); a_init(bar(B_OF, i), 1); a_init(bar(B_OE, i), 4);
+        }
+        a_init(bar(B_PF), 4); a_init(bar(B_PE), 1);                  // (B_PE and index 1 of S/O are unused)
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(a_smem(tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;             // S: 128 columns; O: AHD columns
+    pdl_wait();                                                    // q and the cache rows come from the kernels before
+
+    if (warp == 0 && lane == 0) {
+        // ---- loader ------------------------------------------------------------------------------
+        a_expect(bar(B_Q), ACH * TILE_BYTES);
+        for (int c = 0; c < ACH; ++c)
+            a_tma(a_smem(q_tile + c * TILE_BYTES), &map_q, head * AHD + 64 * c, q_begin + tile * ABM, bar(B_Q));
+        const int* table = block_table + (size_t)seq * table_width;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j & 1;
+            const int key0 = (first_tile + j) * ABN;
+            for (int which = 0; which < 2 && ok; ++which) {           // 0: keys (two stages), 1: values (one stage)
+                const int stage = which ? 0 : s;
+                const uint32_t full = bar(which ? B_VF : B_KF, stage), empty = bar(which ? B_VE : B_KE, stage);
+                if (which == 0 && j >= 2) ok = a_wait(empty, ((j >> 1) - 1) & 1, flag);
+                if (which == 1 && j >= 1) ok = a_wait(empty, (j - 1) & 1, flag);
+                if (!ok) break;
+                uint8_t* dst = which ? v_ring : k_ring + (size_t)s * ACH * TILE_BYTES;
+                a_expect(full, ACH * TILE_BYTES);
+                for (int r = 0; r < ABN; r += rows_per_load) {
+                    const int key = key0 + r;
+                    const int block = table[min(key / block_size, table_width - 1)];
+                    const int row = (block * num_kv_heads + kv_head) * block_size + (key % block_size);
+                    for (int c = 0; c < ACH; ++c)
+                        a_tma(a_smem(dst + c * TILE_BYTES + r * 128), which ? &map_v : &map_k, 64 * c, row, full);
+                }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- tensor-core issue -----------------------------------------------------------------------
+        constexpr uint32_t idesc_s = a_idesc(ABM, ABN, 0), idesc_o = a_idesc(ABM, 64, 1);
+        bool ok = a_wait(bar(B_Q), 0, flag);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j & 1;
+            // S = Q . K_j^T, once the softmax has read the previous tile's scores out
+            if (!a_wait(bar(B_KF, s), (j >> 1) & 1, flag)) { ok = false; break; }
+            if (j >= 1 && !a_wait(bar(B_SE), (j - 1) & 1, flag)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < ACH; ++c) {
+                const uint64_t qd = a_desc(a_smem(q_tile + c * TILE_BYTES));
+                const uint64_t kd = a_desc(a_smem(k_ring + (size_t)(s * ACH + c) * TILE_BYTES));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) a_mma(tmem_s, qd + 2 * k, kd + 2 * k, idesc_s, (c | k) ? 1u : 0u);
+            }
+            a_commit(bar(B_KE, s));
+            a_commit(bar(B_SF));
+            // O_j = P_j . V_j: wait for the probabilities, the values, and the output buffer
+            if (!a_wait(bar(B_PF), j & 1, flag) || !a_wait(bar(B_VF), j & 1, flag)) { ok = false; break; }
+            if (j >= 1 && !a_wait(bar(B_OE), (j - 1) & 1, flag)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {                          // 16 keys per instruction
+                const uint64_t pd = a_desc(a_smem(p_tile + (kk >> 2) * TILE_BYTES)) + 2 * (kk & 3);
+#pragma unroll
+                for (int c = 0; c < ACH; ++c) {
+                    // V tile rows are keys: 16 keys further is 16 x 128 bytes = 128 descriptor units
+                    const uint64_t vd = a_desc(a_smem(v_ring + (size_t)c * TILE_BYTES)) + 128 * kk;
+                    a_mma(tmem_o + (uint32_t)(64 * c), pd, vd, idesc_o, kk ? 1u : 0u);
+                }
+            }
+            a_commit(bar(B_VE));
+            a_commit(bar(B_OF));
+        }
+    } else if (warp >= 2) {
+        // ---- softmax and output: one thread per query row -----------------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                          // row of the tile = TMEM lane
+        const int q_row = tile * ABM + row;                           // index among the sequence's new tokens
+        const int pos = ctx_before + q_row;
+        const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+        const float scale_log2 = scale * 1.4426950408889634f;
+        float o[AHD];
+#pragma unroll
+        for (int d = 0; d < AHD; ++d) o[d] = 0.0f;
+        float row_max = -INFINITY, row_sum = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int key0 = (first_tile + j) * ABN;
+            ok = a_wait(bar(B_SF), j & 1, flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // a row needs masks only in tiles that reach past its own position, past the sequence's end or
+            // below its window; everywhere else the raw scores are used as they are
+            const bool plain = key0 + ABN - 1 <= pos && key0 + ABN - 1 < ctx && (window == 0 || key0 > pos - window);
+            auto visible = [&](int key) { return key <= pos && key < ctx && (window == 0 || key > pos - window); };
+            // pass 1 over the scores (in tensor memory): the row's maximum in this tile, four chains abreast
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+            for (int c = 0; c < ABN; c += 32) {
+                uint32_t v[32];
+                a_ld32(tmem_s + lane_bits + (uint32_t)c, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (plain) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) m4[e & 3] = fmaxf(m4[e & 3], __uint_as_float(v[e]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        m4[e & 3] = fmaxf(m4[e & 3], visible(key0 + c + e) ? __uint_as_float(v[e]) : -INFINITY);
+                }
+            }
+            const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;   // scale > 0
+            const float new_max = fmaxf(row_max, tile_max);
+            const float corr = new_max == -INFINITY ? 1.0f : a_exp2(row_max - new_max);
+            const float offset = new_max == -INFINITY ? 0.0f : new_max;      // all masked so far: every p below is 0
+            row_max = new_max;
+            // pass 2: probabilities, their sum, and the bfloat16 tile for P.V (8 keys = one 16-byte piece).
+            // The product that read the previous tile's probabilities has finished: its output was waited
+            // for at the end of the previous round.
+            float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+            for (int c = 0; c < ABN; c += 32) {
+                uint32_t v[32];
+                a_ld32(tmem_s + lane_bits + (uint32_t)c, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float p[32];
+                if (plain) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) p[e] = a_exp2(fmaf(__uint_as_float(v[e]), scale_log2, -offset));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        p[e] = visible(key0 + c + e) ? a_exp2(fmaf(__uint_as_float(v[e]), scale_log2, -offset)) : 0.0f;
+                }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) s4[e & 3] += p[e];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 pair = __floats2bfloat162_rn(p[8 * q4 + 2 * e], p[8 * q4 + 2 * e + 1]);
+                        packed[e] = *(const uint32_t*)&pair;
+                    }
+                    const int piece = (c >> 3) + q4;                    // 0..15 over the tile's 128 keys
+                    uint8_t* half = p_tile + (piece >> 3) * TILE_BYTES;
+                    *(uint4*)(half + row * 128 + (((piece & 7) ^ (row & 7)) << 4)) =
+                        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                }
+            }
+            row_sum = row_sum * corr + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) { a_arrive(bar(B_SE)); a_arrive(bar(B_PF)); }   // scores read out; probabilities in place
+            // o = o * corr + O_j, read back from tensor memory when the product has finished
+            ok = a_wait(bar(B_OF), j & 1, flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < AHD; c += 32) {
+                uint32_t v[32];
+                a_ld32(tmem_o + lane_bits + (uint32_t)c, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int e = 0; e < 32; ++e) o[c + e] = fmaf(o[c + e], corr, __uint_as_float(v[e]));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) a_arrive(bar(B_OE));
+        }
+        if (ok && q_row < q_len) {
+            const float inverse = 1.0f / row_sum;
+            __nv_bfloat16* dst = out + ((size_t)(q_begin + q_row) * num_heads + head) * AHD;
+#pragma unroll
+            for (int d = 0; d < AHD; d += 8) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(o[d + 2 * e] * inverse, o[d + 2 * e + 1] * inverse);
+                    packed[e] = *(const uint32_t*)&pair;
+                }
+                *(uint4*)(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*AEncode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                            const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                            CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static AEncode a_encoder() {
+    static AEncode fn = [] {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) != cudaSuccess ||
+            result != cudaDriverEntryPointSuccess)
+            entry = nullptr;
+        return (AEncode)entry;
+    }();
+    return fn;
+}
+
+// bfloat16 matrix [rows, cols] row-major, box of box_rows x 64 columns, 128-byte swizzle
+static int a_map(const void* base, long long rows, int cols, int box_rows, CUtensorMap* out) {
+    struct Key { const void* base; long long rows; int cols, box; };
+    static std::mutex lock;
+    static std::vector<std::pair<Key, CUtensorMap>> cache;
+    std::lock_guard<std::mutex> guard(lock);
+    for (auto& entry : cache)
+        if (entry.first.base == base && entry.first.rows == rows && entry.first.cols == cols && entry.first.box == box_rows) {
+            *out = entry.second;
+            return 0;
+        }
+    AEncode encode = a_encoder();
+    if (!encode) return fail("skv_attention_prefill_tc", "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap map;
+    const CUresult status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS) return fail("skv_attention_prefill_tc", "cuTensorMapEncodeTiled failed");
+    if (cache.size() > 1024) cache.clear();
+    cache.push_back({Key{base, rows, cols, box_rows}, map});
+    *out = map;
+    return 0;
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+// As skv_attention_prefill; cache_blocks is the number of blocks of the layer's cache tensors
+// [cache_blocks][kv_heads][block_size][head_dim]; n_tokens the rows of q and out.
+SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, int cache_blocks,
+                                        const int* block_table, int table_width, const int* cu_q,
+                                        const int* ctx_after, void* out, int n_seqs, int n_tokens, int max_q_len,
+                                        int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
+                                        int window, int* flag, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if (head_dim != AHD) return fail("skv_attention_prefill_tc", "this library was built for another head size");
+    if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
+        return fail("skv_attention_prefill_tc", "heads must be a positive multiple of kv heads");
+    if (block_size < 16 || (block_size & (block_size - 1)) != 0)
+        return fail("skv_attention_prefill_tc", "block_size must be a power of two, at least 16");
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
+        return fail("skv_attention_prefill_tc", "operands must be 16-byte aligned");
+    const int rows_per_load = block_size < 128 ? block_size : 128;
+    CUtensorMap map_q, map_k, map_v;
+    if (int code = a_map(q, n_tokens, num_heads * AHD, 128, &map_q)) return code;
+    const long long cache_rows = (long long)cache_blocks * num_kv_heads * block_size;
+    if (int code = a_map(k_cache, cache_rows, AHD, rows_per_load, &map_k)) return code;
+    if (int code = a_map(v_cache, cache_rows, AHD, rows_per_load, &map_v)) return code;
+    const int tiles_per_seq = (max_q_len + ABM - 1) / ABM;
+    const long long blocks = (long long)n_seqs * tiles_per_seq;
+    if (blocks > 0x7fffffffLL || num_heads > 65535) return fail("skv_attention_prefill_tc", "too many tokens or heads");
+    const size_t smem = (size_t)(ACH + 3 * ACH + 2) * TILE_BYTES + B_COUNT * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel,
+                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("skv_attention_prefill_tc", cudaGetErrorString(status));
+        configured = true;
+    }
+    return launch_pdl("skv_attention_prefill_tc", prefill_attention_tc_kernel, dim3((unsigned)blocks, num_heads),
+                      dim3(ATHREADS), smem, stream, map_q, map_k, map_v, block_table, table_width, cu_q, ctx_after,
+                      (__nv_bfloat16*)out, num_heads, num_kv_heads, block_size, rows_per_load, scale, window,
+                      tiles_per_seq, flag);
+}
+
+SKV_EXPORT int skv_has_attention_prefill_tc() { return 1; }
+
+#else
+
+SKV_EXPORT int skv_attention_prefill_tc(const void*, const void*, const void*, int, const int*, int, const int*,
+                                        const int*, void*, int, int, int, int, int, int, int, float, int, int*,
+                                        cudaStream_t) {
+    return skv::fail("skv_attention_prefill_tc", "this build (float32, or a head size other than 64 or 128) has no such kernel");
+}
+
+SKV_EXPORT int skv_has_attention_prefill_tc() { return 0; }
+
+#endif

@@ -21,7 +21,7 @@ import time
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent
-SOURCES = ("elementwise.cu", "linear.cu", "gemm_tcgen05.cu", "attention.cu", "attention_decode.cu", "attention_decode_fused.cu", "attention_prefill.cu", "sampling.cu")
+SOURCES = ("elementwise.cu", "linear.cu", "gemm_tcgen05.cu", "attention.cu", "attention_decode.cu", "attention_decode_fused.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "sampling.cu")
 HEADERS = ("common.cuh",)
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 COMMON_FLAGS = ("-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden")

@@ -184,6 +184,28 @@ class Kernels:
             _ptr(ctx_after), _ptr(out), n_seqs, max_q_len, num_heads, num_kv_heads, head_dim, block_size,
             ctypes.c_float(scale), window, _stream()), "attention_prefill")
 
+    def has_attention_prefill_tc(self) -> bool:
+        return bool(self.lib.skv_has_attention_prefill_tc())
+
+    def attention_prefill_tc(self, q, k_cache, v_cache, block_table, cu_q, ctx_after, out, max_q_len: int,
+                             num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, scale: float,
+                             window: int = 0, flag=None):
+        """``attention_prefill`` with both products on the tcgen05 tensor cores (bfloat16, head size 64 or 128)."""
+        self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
+        self._want(block_table, torch.int32, "block_table"); self._want(cu_q, torch.int32, "cu_q")
+        self._want(ctx_after, torch.int32, "ctx_after")
+        n_seqs = ctx_after.numel()
+        if cu_q.numel() != n_seqs + 1 or block_table.shape[0] != n_seqs:
+            raise KernelError("attention_prefill_tc: one length, one offset pair and one table row per sequence is needed")
+        if tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, head_dim) or k_cache.shape != v_cache.shape:
+            raise KernelError("attention_prefill_tc: the cache must be [blocks, kv_heads, block_size, head_dim]")
+        self._check(self.lib.skv_attention_prefill_tc(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table), block_table.shape[1],
+            _ptr(cu_q), _ptr(ctx_after), _ptr(out), n_seqs, q.shape[0], max_q_len, num_heads, num_kv_heads, head_dim,
+            block_size, ctypes.c_float(scale), window, _ptr(flag if flag is not None else self.error_flag),
+            _stream()), "attention_prefill_tc")
+
     def attention_decode(self, q, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
                          num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
                          splits: int = 1, scratch_o=None, scratch_ml=None):

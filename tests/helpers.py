@@ -30,7 +30,12 @@ TINY_D = dict(architectures=["LlamaForCausalLM"], hidden_size=56, intermediate_s
               num_hidden_layers=2, num_attention_heads=7, num_key_value_heads=1, head_dim=16,
               vocab_size=203, rms_norm_eps=1e-5, rope_theta=1000.0, max_position_embeddings=256,
               tie_word_embeddings=True, hidden_act="silu")
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# Head size 64: the sizes at which the tcgen05 attention and its TMA cache gathers take over.
+TINY_E = dict(architectures=["LlamaForCausalLM"], hidden_size=128, intermediate_size=136,
+              num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1, head_dim=64,
+              vocab_size=300, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=512,
+              tie_word_embeddings=False, hidden_act="silu")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_folder(folder, raw_config, seed, dtype=torch.float32):

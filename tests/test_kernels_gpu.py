@@ -427,3 +427,30 @@ def test_attention_decode_fused_equals_the_separate_kernels(heads, kv_heads, hea
                              block_size, scale, window, splits, False)
     assert torch.equal(k3, k1) and torch.equal(v3, v1)
     torch.testing.assert_close(again.float(), expected.float(), rtol=1.6e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size,lengths,new,window", [
+    (32, 4, 64, 64, [300, 129, 65], [300, 129, 65], 0),       # the TinyLlama head layout
+    (8, 1, 64, 64, [70, 200], [6, 65], 0),                    # continuing prompts that are partly cached
+    (4, 2, 64, 16, [150, 45, 1, 128], [150, 20, 1, 128], 0),  # small cache blocks, tile-aligned and tiny lengths
+    (5, 5, 128, 32, [130, 257], [130, 257], 0),
+    (4, 4, 128, 128, [400], [300], 0),                        # blocks as large as a key tile
+    (4, 2, 64, 16, [300, 45], [300, 20], 70),                 # a window
+    (2, 1, 64, 64, [1000], [1000], 200),                      # a window wider than a key tile
+])
+def test_attention_prefill_tcgen05(heads, kv_heads, head_dim, block_size, lengths, new, window):
+    dtype = torch.bfloat16
+    k = lib(dtype, head_dim)
+    assert k.has_attention_prefill_tc()
+    setup = paged_setup(dtype, lengths, new, heads, kv_heads, head_dim, block_size, seed=3 * heads + head_dim)
+    n = setup["q"].shape[0]
+    out = torch.full((n, heads * head_dim), float("nan"), device="cuda").to(dtype)
+    scale = 0.37 / math.sqrt(head_dim)
+    cu_q = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device="cuda")
+    ctx_after = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    k.attention_prefill_tc(setup["q"].view(n, -1).contiguous(), setup["k_cache"], setup["v_cache"], setup["table"], cu_q,
+                           ctx_after, out, max(new), heads, kv_heads, head_dim, block_size, scale, window)
+    torch.cuda.synchronize()
+    assert int(k.error_flag.item()) == 0
+    ref = attention_reference(setup, dtype, heads, kv_heads, scale, window).view(n, -1)
+    close(out, ref, dtype)
