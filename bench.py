@@ -40,6 +40,13 @@ TINYLLAMA = dict(architectures=["LlamaForCausalLM"], hidden_size=2048, intermedi
                  num_hidden_layers=22, num_attention_heads=32, num_key_value_heads=4, head_dim=64,
                  vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=2048,
                  tie_word_embeddings=False, hidden_act="silu")
+# Larger shapes of the same family (sizes only), for --shape.
+LLAMA2_7B = dict(TINYLLAMA, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32, num_attention_heads=32,
+                 num_key_value_heads=32, head_dim=128, vocab_size=32000, max_position_embeddings=4096)
+LLAMA3_8B = dict(TINYLLAMA, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                 num_key_value_heads=8, head_dim=128, vocab_size=128256, rope_theta=500000.0,
+                 max_position_embeddings=8192)
+SHAPES = {"tinyllama-1.1b": TINYLLAMA, "llama2-7b": LLAMA2_7B, "llama3-8b": LLAMA3_8B}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -105,10 +112,10 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def make_engine(layers: int, max_tokens: int, max_batch: int):
+def make_engine(layers: int, max_tokens: int, max_batch: int, shape=None):
     import torch
     from stratakv_b200 import Engine, EngineConfig, LlamaConfig
-    raw = dict(TINYLLAMA, num_hidden_layers=layers)
+    raw = dict(shape or TINYLLAMA, num_hidden_layers=layers)
     config = LlamaConfig.from_dict(raw)
     engine_config = EngineConfig(max_tokens=max_tokens, dtype="bfloat16", max_batch=max_batch)
     from stratakv_b200.config.registry import resolve_architecture
@@ -217,7 +224,8 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--layers", type=int, default=TINYLLAMA["num_hidden_layers"])
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both are reported)")
+    parser.add_argument("--shape", default="tinyllama-1.1b", choices=sorted(SHAPES))
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     args = parser.parse_args()
@@ -233,14 +241,17 @@ def main() -> int:
     if not torch.cuda.is_available():
         print("bench.py: no CUDA device")
         return 1
-    vocab = TINYLLAMA["vocab_size"]
+    shape = SHAPES[args.shape]
+    if args.layers is None:
+        args.layers = shape["num_hidden_layers"]
+    vocab = shape["vocab_size"]
     start_context = CONTEXT - steps - warmup                 # the timed steps end at the named context
     if start_context < 1:
         print("bench.py: --steps plus --warmup must stay below the context of 2048")
         return 1
     biggest = 64 if not args.skip_points else args.batch
     max_tokens = max(biggest * (CONTEXT + 64), PREFILL_TOKENS + 64)
-    engine, config = make_engine(args.layers, max_tokens, max(biggest, args.batch))
+    engine, config = make_engine(args.layers, max_tokens, max(biggest, args.batch), shape)
     peak = peaks()
 
     sampler = ClockSampler()
@@ -262,16 +273,16 @@ def main() -> int:
                 "kv_bytes": int(kv_bytes)}
 
     result = {
-        "metric": "decode tokens/s (TinyLlama-1.1B shape, bf16, batch 8, context 2048)",
+        "metric": f"decode tokens/s ({args.shape} shape, bf16, batch {args.batch}, context {CONTEXT})",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": value / 33.8,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": value / 33.8 if args.shape == "tinyllama-1.1b" else None,
         "dtype": "bf16", "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
-        "config": {"model": "TinyLlama-1.1B shape", "layers": args.layers, "layers_of_model": TINYLLAMA["num_hidden_layers"],
+        "config": {"model": f"{args.shape} shape", "layers": args.layers, "layers_of_model": shape["num_hidden_layers"],
                    "hidden": config.hidden_size, "heads": config.num_attention_heads,
                    "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
                    "ffn": config.intermediate_size, "vocab": config.vocab_size, "global_batch": args.batch,
                    "seq_len": CONTEXT, "context_at_end": final_context, "parallelism": "single GPU",
-                   "cache_block": engine.cache.block_size, "l2": "inputs larger than L2 (weights 2.2 GB per step)"},
+                   "cache_block": engine.cache.block_size, "l2": f"inputs larger than L2 (weights {engine.model.weight_bytes() / 1e9:.1f} GB per step)"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "impl": "ours",
     }
     if not args.skip_points:
