@@ -59,7 +59,7 @@ __device__ __forceinline__ float rotated(const float* x, const float2* angles, i
     return x[d - HALF] * a.y + x[d] * a.x;
 }
 
-__global__ void __launch_bounds__(FWARPS * 32)
+__global__ void __launch_bounds__(FWARPS * 32, FHD <= 64 ? 2 : 1)
 decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __restrict__ cos_sin,
                               __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                               const int* __restrict__ block_table, int table_width,
@@ -69,7 +69,6 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     extern __shared__ float fused_smem[];             // [warps][16][FPITCH] merge area, then [16][FPITCH] result
     float* result = fused_smem + (size_t)FWARPS * 16 * FPITCH;
     pdl_launch_dependents();
-    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tig = lane & 3;
     const int seq = blockIdx.x;
@@ -92,8 +91,43 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     const float* token = qkv + (size_t)seq * (q_dim + 2 * kv_dim);
     const float2* angles = cos_sin ? cos_sin + (size_t)pos * (FHD / 2) : nullptr;
 
-    // the block whose split holds the newest position puts that token's key and value in the cache
+    // One group of 16 keys: the lane's share of its keys (for Q.K^T) and values (for P.V), in registers.
+    struct GroupData { uint2 kb[2][FKSTEPS]; uint32_t vw[4][FVWORDS]; };
+    auto load_group = [&](int group, GroupData& data) {
+        const int j0 = group << 4;
+        const int block = table[j0 / block_size];
+        const size_t base = ((size_t)(block * num_kv_heads + kv_head) * block_size + (j0 % block_size)) * FHD;
+        const __nv_bfloat16* k_rows = k_cache + base;
+        const __nv_bfloat16* v_rows = v_cache + base;
+        const int keys[4] = {2 * tig, 2 * tig + 1, 2 * tig + 8, 2 * tig + 9};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const bool live = j0 + keys[i] < ctx;
+            const uint32_t* src = (const uint32_t*)(v_rows + (size_t)keys[i] * FHD + g * (FHD / 8));
+#pragma unroll
+            for (int w = 0; w < FVWORDS; ++w) data.vw[i][w] = live ? src[w] : 0u;
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const bool live = j0 + 8 * t + g < ctx;
+            const __nv_bfloat16* key_row = k_rows + (size_t)(8 * t + g) * FHD + 4 * tig;
+#pragma unroll
+            for (int step = 0; step < FKSTEPS; ++step)
+                data.kb[t][step] = live ? *(const uint2*)(key_row + 16 * step) : make_uint2(0u, 0u);
+        }
+    };
+    // Keys and values of earlier positions were written by earlier steps, so the warp's first group can be
+    // fetched before waiting for the kernel in front (the q|k|v projection): the loads overlap its end.  Not
+    // the group that holds the new position, and not for a layer that reads a cache another layer of this
+    // same step writes (write_kv == 0).
     const int newest_group = pos >> 4;
+    const int first_mine = my_first + warp;
+    const bool prefetched = write_kv && first_mine < my_end && first_mine != newest_group;
+    GroupData ahead;
+    if (prefetched) load_group(first_mine, ahead);
+    pdl_wait();
+
+    // the block whose split holds the newest position puts that token's key and value in the cache
     if (write_kv && newest_group >= my_first && newest_group < my_end) {
         const int block = table[pos / block_size];
         const size_t at = ((size_t)(block * num_kv_heads + kv_head) * block_size + (pos % block_size)) * FHD;
@@ -131,34 +165,18 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     for (int j = 0; j < FOTILES; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
 
-    for (int group = my_first + warp; group < my_end; group += FWARPS) {
+    for (int group = first_mine; group < my_end; group += FWARPS) {
         const int j0 = group << 4;
-        const int block = table[j0 / block_size];
-        const size_t base = ((size_t)(block * num_kv_heads + kv_head) * block_size + (j0 % block_size)) * FHD;
-        const __nv_bfloat16* k_rows = k_cache + base;
-        const __nv_bfloat16* v_rows = v_cache + base;
-        uint32_t vw[4][FVWORDS];
-        {
-            const int keys[4] = {2 * tig, 2 * tig + 1, 2 * tig + 8, 2 * tig + 9};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const bool live = j0 + keys[i] < ctx;
-                const uint32_t* src = (const uint32_t*)(v_rows + (size_t)keys[i] * FHD + g * (FHD / 8));
-#pragma unroll
-                for (int w = 0; w < FVWORDS; ++w) vw[i][w] = live ? src[w] : 0u;
-            }
-        }
+        GroupData data;
+        if (group == first_mine && prefetched) data = ahead;
+        else load_group(group, data);
         float s[2][4];
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
             s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.0f;
-            const bool live = j0 + 8 * t + g < ctx;
-            const __nv_bfloat16* key_row = k_rows + (size_t)(8 * t + g) * FHD + 4 * tig;
 #pragma unroll
-            for (int step = 0; step < FKSTEPS; ++step) {
-                const uint2 kb = live ? *(const uint2*)(key_row + 16 * step) : make_uint2(0u, 0u);
-                f_mma(s[t], qa[step][0], qa[step][1], qa[step][2], qa[step][3], kb.x, kb.y);
-            }
+            for (int step = 0; step < FKSTEPS; ++step)
+                f_mma(s[t], qa[step][0], qa[step][1], qa[step][2], qa[step][3], data.kb[t][step].x, data.kb[t][step].y);
         }
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -201,10 +219,10 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
         const uint32_t a2 = f_pack(p[1][0], p[1][1]), a3 = f_pack(p[1][2], p[1][3]);
 #pragma unroll
         for (int w = 0; w < FVWORDS; ++w) {
-            f_mma(o[2 * w], a0, a1, a2, a3, __byte_perm(vw[0][w], vw[1][w], 0x5410),
-                  __byte_perm(vw[2][w], vw[3][w], 0x5410));
-            f_mma(o[2 * w + 1], a0, a1, a2, a3, __byte_perm(vw[0][w], vw[1][w], 0x7632),
-                  __byte_perm(vw[2][w], vw[3][w], 0x7632));
+            f_mma(o[2 * w], a0, a1, a2, a3, __byte_perm(data.vw[0][w], data.vw[1][w], 0x5410),
+                  __byte_perm(data.vw[2][w], data.vw[3][w], 0x5410));
+            f_mma(o[2 * w + 1], a0, a1, a2, a3, __byte_perm(data.vw[0][w], data.vw[1][w], 0x7632),
+                  __byte_perm(data.vw[2][w], data.vw[3][w], 0x7632));
         }
     }
     // merge the warps into `result`: rows x (head_dim outputs, max, sum)

@@ -55,6 +55,42 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         row_out[c] = from_float<T>(row[c] * inverse_rms * gamma[c]);
 }
 
+// The same with one warp per row and 16-byte loads, for steps with many rows (hidden % 4 == 0):
+// the row is read twice, the second time from L1.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma, float eps,
+                    T* __restrict__ out, const int* __restrict__ rows, int n_rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= n_rows) return;
+    const int src = rows ? rows[r] : r;
+    const float4* row = (const float4*)(x + (size_t)src * hidden);
+    const int quads = hidden >> 2;
+    float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int i = lane; i < quads; i += 32) {
+        const float4 v = row[i];
+        partial[0] = fmaf(v.x, v.x, partial[0]); partial[1] = fmaf(v.y, v.y, partial[1]);
+        partial[2] = fmaf(v.z, v.z, partial[2]); partial[3] = fmaf(v.w, v.w, partial[3]);
+    }
+    const float mean_square = warp_sum((partial[0] + partial[1]) + (partial[2] + partial[3])) / (float)hidden;
+    const float inverse_rms = 1.0f / sqrtf(mean_square + eps);
+    T* row_out = out + (size_t)r * hidden;
+    const float4* g4 = (const float4*)gamma;
+    for (int i = lane; i < quads; i += 32) {
+        const float4 v = row[i], g = g4[i];
+        const float y0 = v.x * inverse_rms * g.x, y1 = v.y * inverse_rms * g.y;
+        const float y2 = v.z * inverse_rms * g.z, y3 = v.w * inverse_rms * g.w;
+        if (sizeof(T) == 4) {
+            ((float4*)row_out)[i] = make_float4(y0, y1, y2, y3);
+        } else {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+            ((uint2*)row_out)[i] = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // One token per block.  Rotates every query head and key head with split-half
 // pairs (i, i + head_dim/2) (src/layers/attention.cpp:96-135), writes queries
@@ -111,6 +147,66 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const float2
     }
 }
 
+// The same with four pairs (and four values) per thread and 16-byte loads; head_dim % 8 == 0.
+template <typename T>
+__device__ __forceinline__ void store4(T* dst, float a, float b, float c, float d) {
+    if (sizeof(T) == 4) {
+        *(float4*)dst = make_float4(a, b, c, d);
+    } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        *(uint2*)dst = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_kv_write_vec_kernel(const float* __restrict__ qkv, const float2* __restrict__ cos_sin,
+                         const int* __restrict__ positions, const int* __restrict__ token_seq,
+                         const int* __restrict__ block_table, int table_width, T* __restrict__ q_out,
+                         T* __restrict__ k_cache, T* __restrict__ v_cache, int num_heads, int num_kv_heads,
+                         int head_dim, int block_size, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1, quads = half >> 2;
+    const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
+    const int pos = positions[t];
+    const float* src = qkv + (size_t)t * (q_dim + 2 * kv_dim);
+    const float4* angles = cos_sin ? (const float4*)(cos_sin + (size_t)pos * half) : nullptr;
+    size_t tile_base = 0;
+    if (write_kv) {
+        const int seq = token_seq[t];
+        const int block = block_table[(size_t)seq * table_width + pos / block_size];
+        tile_base = ((size_t)block * num_kv_heads * block_size + (pos % block_size)) * head_dim;
+    }
+    const int rotary_heads = num_heads + (write_kv ? num_kv_heads : 0);
+    for (int idx = threadIdx.x; idx < rotary_heads * quads; idx += blockDim.x) {
+        const int head = idx / quads, i = (idx - head * quads) << 2;
+        const float* x = src + (size_t)head * head_dim;
+        const float4 x1 = *(const float4*)(x + i), x2 = *(const float4*)(x + i + half);
+        float4 c = make_float4(1.0f, 1.0f, 1.0f, 1.0f), s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (angles) {
+            const float4 a = angles[i >> 1], b = angles[(i >> 1) + 1];      // (cos, sin) pairs i..i+1 and i+2..i+3
+            c = make_float4(a.x, a.z, b.x, b.z);
+            s = make_float4(a.y, a.w, b.y, b.w);
+        }
+        T* dst = head < num_heads ? q_out + (size_t)t * q_dim + (size_t)head * head_dim
+                                  : k_cache + tile_base + (size_t)(head - num_heads) * block_size * head_dim;
+        store4<T>(dst + i, x1.x * c.x - x2.x * s.x, x1.y * c.y - x2.y * s.y, x1.z * c.z - x2.z * s.z,
+                  x1.w * c.w - x2.w * s.w);
+        store4<T>(dst + i + half, x1.x * s.x + x2.x * c.x, x1.y * s.y + x2.y * c.y, x1.z * s.z + x2.z * c.z,
+                  x1.w * s.w + x2.w * c.w);
+    }
+    if (write_kv) {
+        const float* v = src + q_dim + kv_dim;
+        for (int idx = threadIdx.x; idx < kv_dim >> 2; idx += blockDim.x) {
+            const int e = idx << 2, g = e / head_dim, d = e - g * head_dim;
+            const float4 value = *(const float4*)(v + e);
+            store4<T>(v_cache + tile_base + (size_t)g * block_size * head_dim + d, value.x, value.y, value.z, value.w);
+        }
+    }
+}
+
 // out[i] += in[i]  (float residual stream; used by parts that have no fused epilogue)
 __global__ void add_inplace_kernel(float* __restrict__ out, const float* __restrict__ in, size_t n) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -138,6 +234,9 @@ SKV_EXPORT int skv_rmsnorm(const float* x, const float* gamma, float eps, void* 
                            int n_rows, int hidden, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (hidden <= 0) return fail("skv_rmsnorm", "hidden must be positive");
+    if (n_rows >= 64 && hidden % 4 == 0 && (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out) & 15) == 0)
+        return launch_pdl("skv_rmsnorm", rmsnorm_rows_kernel<skv_t>, dim3((n_rows + 7) / 8), dim3(256), 0, stream, x,
+                          gamma, eps, (skv_t*)out, rows, n_rows, hidden);
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     return launch_pdl("skv_rmsnorm", rmsnorm_kernel<skv_t>, dim3(n_rows), dim3(threads), 0, stream, x, gamma, eps,
                       (skv_t*)out, rows, hidden);
@@ -152,6 +251,11 @@ SKV_EXPORT int skv_rope_kv_write(const float* qkv, const float* cos_sin, const i
     if (head_dim <= 0 || (head_dim & 1)) return fail("skv_rope_kv_write", "head_dim must be positive and even");
     if (num_heads <= 0 || num_kv_heads <= 0 || block_size <= 0)
         return fail("skv_rope_kv_write", "head counts and block_size must be positive");
+    if (head_dim % 8 == 0 && (((uintptr_t)qkv | (uintptr_t)cos_sin | (uintptr_t)q_out | (uintptr_t)k_cache |
+                               (uintptr_t)v_cache) & 15) == 0)
+        return launch_pdl("skv_rope_kv_write", rope_kv_write_vec_kernel<skv_t>, dim3(n_tokens), dim3(128), 0, stream,
+                          qkv, (const float2*)cos_sin, positions, token_seq, block_table, table_width, (skv_t*)q_out,
+                          (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv);
     return launch_pdl("skv_rope_kv_write", rope_kv_write_kernel<skv_t>, dim3(n_tokens), dim3(128), 0, stream, qkv,
                       (const float2*)cos_sin, positions, token_seq, block_table, table_width, (skv_t*)q_out,
                       (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv);

@@ -35,7 +35,8 @@ def test_embed(dtype, vocab, hidden, n):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,hidden,eps", [(5, 80, 1e-5), (3, 2048, 1e-6), (9, 1000, 3e-3)])
+@pytest.mark.parametrize("rows,hidden,eps", [(5, 80, 1e-5), (3, 2048, 1e-6), (9, 1000, 3e-3), (100, 264, 1e-5),
+                                             (70, 2048, 1e-6), (65, 82, 1e-5)])
 def test_rmsnorm(dtype, rows, hidden, eps):
     k = lib(dtype)
     x = torch.randn(rows, hidden, device="cuda") * 3.0
