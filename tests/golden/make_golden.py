@@ -6,7 +6,7 @@ tests/golden/golden_driver.cpp against it, runs a tiny Llama (2 layers, hidden 6
 reference fixes in code, theta 10000 and eps 1e-5) through the reference's own classes for
 three prompts, and stores the logits of every position.
 
-    python tests/golden/make_golden.py [path of the reference checkout, default /root/reference]
+    python tests/golden/make_golden.py PATH_OF_THE_REFERENCE_CHECKOUT
 """
 import json
 import subprocess
@@ -25,7 +25,9 @@ PROMPT_LENGTHS = (5, 9, 13)
 
 
 def main():
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    reference = Path(sys.argv[1])
     work = Path(tempfile.mkdtemp(prefix="stratakv_golden_"))
     build = work / "build"
     subprocess.run(["cmake", "-S", str(reference), "-B", str(build), "-DSTRATAKV_CUDA=OFF",
