@@ -3,19 +3,21 @@
 //
 // It does the arithmetic of attention_prefill.cu (src/layers/attention.cpp:261-338 in the
 // reference, which has no prefill kernel at all) with another division of labour.  A block takes
-// 128 queries of one head; keys and values come in tiles of 128 positions:
+// 128 queries of one head; keys and values come in tiles of 64 positions:
 //   warp 0   one thread: TMA loads of the Q tile (once) and of K and V tiles into two-stage rings;
 //            a tile is gathered from the cache blocks the sequence's block table names;
-//   warp 1   one thread: S = Q.K^T (128 x 128 x head_dim) into the score buffer in tensor memory,
-//            and O_j = P.V (128 x head_dim x 128) into the output buffer;
+//   warp 1   one thread: S = Q.K^T (128 x 64 x head_dim) into one of two score buffers in tensor
+//            memory (the next tile's scores are issued before this tile's output product), and
+//            O += P.V (128 x head_dim x 64) into the output accumulator, also in tensor memory;
 //            V is used as it lies in the cache (positions x head_dim), as an MN-major operand;
-//   warps 2-5  one thread per query row: read the scores with tcgen05.ld, mask, running maximum,
-//            2^x on the special-function unit (scores carry log2 e), row sums, probabilities as
-//            bfloat16 into a swizzled shared-memory tile (the A operand of P.V), and the running
-//            output in registers: O = O * 2^(m_old - m_new) + O_j, read back from tensor memory.
-// The softmax is the long pole (one warp per scheduler runs its dependent chains at a fraction of the
-// issue rate), so a block uses only half of the SM's tensor memory and shared memory and two blocks
-// share an SM: while one block's rows are in the softmax the other's products run.  Every mbarrier
+//   warps 2-5  one thread per query row: read the scores with tcgen05.ld, mask, 2^x on the
+//            special-function unit (scores carry log2 e), row sums, probabilities as bfloat16 into
+//            one of two swizzled shared-memory tiles (the A operand of P.V).  The maximum the
+//            exponentials are taken against is raised only when a tile exceeds it by 2^8; only then
+//            is the accumulated output rescaled (tcgen05.ld / st), so most tiles never touch it.
+//            At the end the output is read once, divided by the row sum and stored.
+// The softmax is the long pole, so a block uses only half of the SM's tensor memory and shared
+// memory and (for head size 64) two blocks share an SM.  Every mbarrier
 // wait is bounded; on time-out bit 2 (value 4) of the flag word is raised and the block drains.
 #include "common.cuh"
 
@@ -31,10 +33,11 @@ namespace skv {
 
 constexpr int AHD = SKV_HEAD_DIM;
 constexpr int ACH = AHD / 64;                       // 64-wide (128-byte) chunks of a head
-constexpr int ABM = 128, ABN = 128;                 // queries and keys per tile
+constexpr int ABM = 128, ABN = 64;                  // queries and keys per tile
 constexpr int ATHREADS = 192;
 constexpr uint32_t AWAIT = 1u << 20;
 constexpr uint32_t TILE_BYTES = 128 * 128;          // one 128-row x 128-byte swizzled tile
+constexpr uint32_t KV_TILE_BYTES = ABN * 128;       // one 64-row tile of keys or values
 
 __device__ __forceinline__ uint32_t a_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void a_init(uint32_t bar, uint32_t count) {
@@ -97,10 +100,27 @@ __device__ __forceinline__ float a_exp2(float x) {
     return y;
 }
 
-enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PE = 14, B_OF = 15,
-       B_OE = 17, B_COUNT = 19 };
+__device__ __forceinline__ void a_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
 
-__global__ void __launch_bounds__(ATHREADS, 2)
+// barriers: Q; for each of two stages K full/empty, V full/empty, S full/empty, P full/empty
+enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PE = 15, B_COUNT = 17 };
+
+// The running maximum a row's exponentials are taken against is only raised when a tile's maximum
+// exceeds it by more than this many powers of two; until then the accumulated output (in tensor
+// memory) needs no rescaling and probabilities stay below 2^RESCALE_MARGIN.
+constexpr float RESCALE_MARGIN = 8.0f;
+
+__global__ void __launch_bounds__(ATHREADS, AHD <= 64 ? 2 : 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_after,
@@ -108,11 +128,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             int rows_per_load, float scale, int window, int tiles_per_seq, int* __restrict__ flag) {
     extern __shared__ uint8_t a_raw[];
     uint8_t* base = (uint8_t*)(((uintptr_t)a_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* q_tile = base;                                        // ACH tiles
-    uint8_t* k_ring = q_tile + ACH * TILE_BYTES;                   // 2 stages x ACH tiles
-    uint8_t* v_ring = k_ring + 2 * ACH * TILE_BYTES;               // 1 stage x ACH tiles
-    uint8_t* p_tile = v_ring + ACH * TILE_BYTES;                   // 2 tiles (keys 0-63, 64-127)
-    uint64_t* bars = (uint64_t*)(p_tile + 2 * TILE_BYTES);
+    uint8_t* q_tile = base;                                        // ACH tiles of 128 rows
+    uint8_t* k_ring = q_tile + ACH * TILE_BYTES;                   // 2 stages x ACH tiles of 64 rows
+    uint8_t* v_ring = k_ring + 2 * ACH * KV_TILE_BYTES;            // 2 stages x ACH tiles of 64 rows
+    uint8_t* p_ring = v_ring + 2 * ACH * KV_TILE_BYTES;            // 2 tiles of 128 rows (64 keys = 128 bytes a row)
+    uint64_t* bars = (uint64_t*)(p_ring + 2 * TILE_BYTES);
     uint32_t* tmem_slot = (uint32_t*)(bars + B_COUNT);
     const uint32_t bar0 = a_smem(bars);
     auto bar = [&](int which, int index = 0) { return bar0 + 8u * (uint32_t)(which + index); };
@@ -134,9 +154,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         a_init(bar(B_Q), 1);
         for (int i = 0; i < 2; ++i) {
             a_init(bar(B_KF, i), 1); a_init(bar(B_KE, i), 1); a_init(bar(B_VF, i), 1); a_init(bar(B_VE, i), 1);
-            a_init(bar(B_SF, i), 1); a_init(bar(B_SE, i), 4); a_init(bar(B_OF, i), 1); a_init(bar(B_OE, i), 4);
+            a_init(bar(B_SF, i), 1); a_init(bar(B_SE, i), 4); a_init(bar(B_PF, i), 4); a_init(bar(B_PE, i), 1);
         }
-        a_init(bar(B_PF), 4); a_init(bar(B_PE), 1);                  // (B_PE and index 1 of S/O are unused)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -148,7 +167,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;             // S: 128 columns; O: AHD columns
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;             // S: 2 x 64 columns; O: AHD columns
     pdl_wait();                                                    // q and the cache rows come from the kernels before
 
     if (warp == 0 && lane == 0) {
@@ -161,20 +180,18 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int s = j & 1;
             const int key0 = (first_tile + j) * ABN;
-            for (int which = 0; which < 2 && ok; ++which) {           // 0: keys (two stages), 1: values (one stage)
-                const int stage = which ? 0 : s;
-                const uint32_t full = bar(which ? B_VF : B_KF, stage), empty = bar(which ? B_VE : B_KE, stage);
-                if (which == 0 && j >= 2) ok = a_wait(empty, ((j >> 1) - 1) & 1, flag);
-                if (which == 1 && j >= 1) ok = a_wait(empty, (j - 1) & 1, flag);
+            for (int which = 0; which < 2 && ok; ++which) {           // 0: keys, 1: values
+                const uint32_t full = bar(which ? B_VF : B_KF, s), empty = bar(which ? B_VE : B_KE, s);
+                if (j >= 2) ok = a_wait(empty, ((j >> 1) - 1) & 1, flag);
                 if (!ok) break;
-                uint8_t* dst = which ? v_ring : k_ring + (size_t)s * ACH * TILE_BYTES;
-                a_expect(full, ACH * TILE_BYTES);
+                uint8_t* dst = (which ? v_ring : k_ring) + (size_t)s * ACH * KV_TILE_BYTES;
+                a_expect(full, ACH * KV_TILE_BYTES);
                 for (int r = 0; r < ABN; r += rows_per_load) {
                     const int key = key0 + r;
                     const int block = table[min(key / block_size, table_width - 1)];
                     const int row = (block * num_kv_heads + kv_head) * block_size + (key % block_size);
                     for (int c = 0; c < ACH; ++c)
-                        a_tma(a_smem(dst + c * TILE_BYTES + r * 128), which ? &map_v : &map_k, 64 * c, row, full);
+                        a_tma(a_smem(dst + c * KV_TILE_BYTES + r * 128), which ? &map_v : &map_k, 64 * c, row, full);
                 }
             }
         }
@@ -182,37 +199,42 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---- tensor-core issue -----------------------------------------------------------------------
         constexpr uint32_t idesc_s = a_idesc(ABM, ABN, 0), idesc_o = a_idesc(ABM, 64, 1);
         bool ok = a_wait(bar(B_Q), 0, flag);
-        for (int j = 0; j < n_tiles && ok; ++j) {
+        auto issue_s = [&](int j) {                                  // S[j & 1] = Q . K_j^T
             const int s = j & 1;
-            // S = Q . K_j^T, once the softmax has read the previous tile's scores out
-            if (!a_wait(bar(B_KF, s), (j >> 1) & 1, flag)) { ok = false; break; }
-            if (j >= 1 && !a_wait(bar(B_SE), (j - 1) & 1, flag)) { ok = false; break; }
+            if (!a_wait(bar(B_KF, s), (j >> 1) & 1, flag)) return false;
+            if (j >= 2 && !a_wait(bar(B_SE, s), ((j >> 1) - 1) & 1, flag)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int c = 0; c < ACH; ++c) {
                 const uint64_t qd = a_desc(a_smem(q_tile + c * TILE_BYTES));
-                const uint64_t kd = a_desc(a_smem(k_ring + (size_t)(s * ACH + c) * TILE_BYTES));
+                const uint64_t kd = a_desc(a_smem(k_ring + (size_t)(s * ACH + c) * KV_TILE_BYTES));
 #pragma unroll
-                for (int k = 0; k < 4; ++k) a_mma(tmem_s, qd + 2 * k, kd + 2 * k, idesc_s, (c | k) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k) a_mma(tmem_s + 64u * s, qd + 2 * k, kd + 2 * k, idesc_s, (c | k) ? 1u : 0u);
             }
             a_commit(bar(B_KE, s));
-            a_commit(bar(B_SF));
-            // O_j = P_j . V_j: wait for the probabilities, the values, and the output buffer
-            if (!a_wait(bar(B_PF), j & 1, flag) || !a_wait(bar(B_VF), j & 1, flag)) { ok = false; break; }
-            if (j >= 1 && !a_wait(bar(B_OE), (j - 1) & 1, flag)) { ok = false; break; }
+            a_commit(bar(B_SF, s));
+            return true;
+        };
+        if (ok && n_tiles > 0) ok = issue_s(0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j & 1;
+            if (j + 1 < n_tiles) ok = issue_s(j + 1);                 // the next scores run under this tile's softmax
+            if (!ok) break;
+            // O += P_j . V_j once the probabilities and the values are in shared memory
+            if (!a_wait(bar(B_PF, s), (j >> 1) & 1, flag) || !a_wait(bar(B_VF, s), (j >> 1) & 1, flag)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {                          // 16 keys per instruction
-                const uint64_t pd = a_desc(a_smem(p_tile + (kk >> 2) * TILE_BYTES)) + 2 * (kk & 3);
+            for (int kk = 0; kk < ABN / 16; ++kk) {                   // 16 keys per instruction
+                const uint64_t pd = a_desc(a_smem(p_ring + s * TILE_BYTES)) + 2 * kk;
 #pragma unroll
                 for (int c = 0; c < ACH; ++c) {
                     // V tile rows are keys: 16 keys further is 16 x 128 bytes = 128 descriptor units
-                    const uint64_t vd = a_desc(a_smem(v_ring + (size_t)c * TILE_BYTES)) + 128 * kk;
-                    a_mma(tmem_o + (uint32_t)(64 * c), pd, vd, idesc_o, kk ? 1u : 0u);
+                    const uint64_t vd = a_desc(a_smem(v_ring + (size_t)(s * ACH + c) * KV_TILE_BYTES)) + 128 * kk;
+                    a_mma(tmem_o + (uint32_t)(64 * c), pd, vd, idesc_o, (j | kk) ? 1u : 0u);
                 }
             }
-            a_commit(bar(B_VE));
-            a_commit(bar(B_OF));
+            a_commit(bar(B_VE, s));
+            a_commit(bar(B_PE, s));                                   // also: the output holds tiles 0..j now
         }
     } else if (warp >= 2) {
         // ---- softmax and output: one thread per query row -----------------------------------------
@@ -222,108 +244,114 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos = ctx_before + q_row;
         const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
         const float scale_log2 = scale * 1.4426950408889634f;
-        float o[AHD];
-#pragma unroll
-        for (int d = 0; d < AHD; ++d) o[d] = 0.0f;
-        float row_max = -INFINITY, row_sum = 0.0f;
+        float used_max = -INFINITY, row_sum = 0.0f;                   // in units of log2, after the scale
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j & 1;
             const int key0 = (first_tile + j) * ABN;
-            ok = a_wait(bar(B_SF), j & 1, flag);
+            ok = a_wait(bar(B_SF, s), (j >> 1) & 1, flag);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // a row needs masks only in tiles that reach past its own position, past the sequence's end or
             // below its window; everywhere else the raw scores are used as they are
             const bool plain = key0 + ABN - 1 <= pos && key0 + ABN - 1 < ctx && (window == 0 || key0 > pos - window);
             auto visible = [&](int key) { return key <= pos && key < ctx && (window == 0 || key > pos - window); };
-            // pass 1 over the scores (in tensor memory): the row's maximum in this tile, four chains abreast
+            uint32_t v0[32], v1[32];                                  // the row's 64 scores
+            a_ld32(tmem_s + lane_bits + (uint32_t)(64 * s), v0);
+            a_ld32(tmem_s + lane_bits + (uint32_t)(64 * s + 32), v1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) a_arrive(bar(B_SE, s));                     // the scores are in registers
+            float sc[ABN];
+            if (plain) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) { sc[e] = __uint_as_float(v0[e]); sc[32 + e] = __uint_as_float(v1[e]); }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    sc[e] = visible(key0 + e) ? __uint_as_float(v0[e]) : -INFINITY;
+                    sc[32 + e] = visible(key0 + 32 + e) ? __uint_as_float(v1[e]) : -INFINITY;
+                }
+            }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-            for (int c = 0; c < ABN; c += 32) {
-                uint32_t v[32];
-                a_ld32(tmem_s + lane_bits + (uint32_t)c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (plain) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) m4[e & 3] = fmaxf(m4[e & 3], __uint_as_float(v[e]));
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        m4[e & 3] = fmaxf(m4[e & 3], visible(key0 + c + e) ? __uint_as_float(v[e]) : -INFINITY);
-                }
-            }
+            for (int e = 0; e < ABN; ++e) m4[e & 3] = fmaxf(m4[e & 3], sc[e]);
             const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;   // scale > 0
-            const float new_max = fmaxf(row_max, tile_max);
-            const float corr = new_max == -INFINITY ? 1.0f : a_exp2(row_max - new_max);
-            const float offset = new_max == -INFINITY ? 0.0f : new_max;      // all masked so far: every p below is 0
-            row_max = new_max;
-            // pass 2: probabilities, their sum, and the bfloat16 tile for P.V (8 keys = one 16-byte piece).
-            // The product that read the previous tile's probabilities has finished: its output was waited
-            // for at the end of the previous round.
-            float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // raise the maximum in use (and rescale what has been accumulated) only when it matters
+            const bool raise = tile_max > used_max + RESCALE_MARGIN;
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                // the output accumulator may be touched once the product of the previous tile has finished
+                ok = a_wait(bar(B_PE, (j - 1) & 1), ((j - 1) >> 1) & 1, flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float corr = raise ? a_exp2(used_max - tile_max) : 1.0f;     // 0 if nothing was seen before
 #pragma unroll 1
-            for (int c = 0; c < ABN; c += 32) {
-                uint32_t v[32];
-                a_ld32(tmem_s + lane_bits + (uint32_t)c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float p[32];
-                if (plain) {
+                for (int c = 0; c < AHD; c += 32) {
+                    uint32_t v[32];
+                    a_ld32(tmem_o + lane_bits + (uint32_t)c, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) p[e] = a_exp2(fmaf(__uint_as_float(v[e]), scale_log2, -offset));
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        p[e] = visible(key0 + c + e) ? a_exp2(fmaf(__uint_as_float(v[e]), scale_log2, -offset)) : 0.0f;
+                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * corr);
+                    a_st32(tmem_o + lane_bits + (uint32_t)c, v);
                 }
-#pragma unroll
-                for (int e = 0; e < 32; ++e) s4[e & 3] += p[e];
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint32_t packed[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 pair = __floats2bfloat162_rn(p[8 * q4 + 2 * e], p[8 * q4 + 2 * e + 1]);
-                        packed[e] = *(const uint32_t*)&pair;
-                    }
-                    const int piece = (c >> 3) + q4;                    // 0..15 over the tile's 128 keys
-                    uint8_t* half = p_tile + (piece >> 3) * TILE_BYTES;
-                    *(uint4*)(half + row * 128 + (((piece & 7) ^ (row & 7)) << 4)) =
-                        make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                row_sum *= corr;
             }
-            row_sum = row_sum * corr + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+            if (raise) used_max = tile_max;
+            const float offset = used_max == -INFINITY ? 0.0f : used_max;      // nothing visible yet: every p is 0
+            // the probability buffer may be rewritten once the product two tiles back has read it
+            if (j >= 2) ok = a_wait(bar(B_PE, s), ((j >> 1) - 1) & 1, flag);
+            if (!ok) break;
+            uint8_t* p_tile = p_ring + s * TILE_BYTES;
+            float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int piece = 0; piece < ABN / 8; ++piece) {             // 8 keys = one 16-byte piece
+                float p[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float x = sc[8 * piece + e];
+                    p[e] = (plain || x != -INFINITY) ? a_exp2(fmaf(x, scale_log2, -offset)) : 0.0f;
+                    s4[e & 3] += p[e];
+                }
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+                    packed[e] = *(const uint32_t*)&pair;
+                }
+                *(uint4*)(p_tile + row * 128 + ((piece ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            row_sum += (s4[0] + s4[1]) + (s4[2] + s4[3]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) { a_arrive(bar(B_SE)); a_arrive(bar(B_PF)); }   // scores read out; probabilities in place
-            // o = o * corr + O_j, read back from tensor memory when the product has finished
-            ok = a_wait(bar(B_OF), j & 1, flag);
-            if (!ok) break;
+            if (lane == 0) a_arrive(bar(B_PF, s));                     // probabilities in place (and any rescale done)
+        }
+        // the last product has finished: read the output once, normalise, store
+        if (ok && n_tiles > 0) ok = a_wait(bar(B_PE, (n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, flag);
+        if (ok && n_tiles > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
+            const float inverse = 1.0f / row_sum;
+            __nv_bfloat16* dst = out + ((size_t)(q_begin + min(q_row, q_len - 1)) * num_heads + head) * AHD;
+#pragma unroll 1
             for (int c = 0; c < AHD; c += 32) {
                 uint32_t v[32];
                 a_ld32(tmem_o + lane_bits + (uint32_t)c, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (q_row < q_len) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) o[c + e] = fmaf(o[c + e], corr, __uint_as_float(v[e]));
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) a_arrive(bar(B_OE));
-        }
-        if (ok && q_row < q_len) {
-            const float inverse = 1.0f / row_sum;
-            __nv_bfloat16* dst = out + ((size_t)(q_begin + q_row) * num_heads + head) * AHD;
+                    for (int d = 0; d < 32; d += 8) {
+                        uint32_t packed[4];
 #pragma unroll
-            for (int d = 0; d < AHD; d += 8) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const __nv_bfloat162 pair = __floats2bfloat162_rn(o[d + 2 * e] * inverse, o[d + 2 * e + 1] * inverse);
-                    packed[e] = *(const uint32_t*)&pair;
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[d + 2 * e]) * inverse,
+                                                                              __uint_as_float(v[d + 2 * e + 1]) * inverse);
+                            packed[e] = *(const uint32_t*)&pair;
+                        }
+                        *(uint4*)(dst + c + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
                 }
-                *(uint4*)(dst + d) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
         }
     }
@@ -399,7 +427,7 @@ SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, cons
         return fail("skv_attention_prefill_tc", "block_size must be a power of two, at least 16");
     if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
         return fail("skv_attention_prefill_tc", "operands must be 16-byte aligned");
-    const int rows_per_load = block_size < 128 ? block_size : 128;
+    const int rows_per_load = block_size < ABN ? block_size : ABN;
     CUtensorMap map_q, map_k, map_v;
     if (int code = a_map(q, n_tokens, num_heads * AHD, 128, &map_q)) return code;
     const long long cache_rows = (long long)cache_blocks * num_kv_heads * block_size;
@@ -408,7 +436,7 @@ SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, cons
     const int tiles_per_seq = (max_q_len + ABM - 1) / ABM;
     const long long blocks = (long long)n_seqs * tiles_per_seq;
     if (blocks > 0x7fffffffLL || num_heads > 65535) return fail("skv_attention_prefill_tc", "too many tokens or heads");
-    const size_t smem = (size_t)(ACH + 3 * ACH + 2) * TILE_BYTES + B_COUNT * 8 + 16 + 1024;
+    const size_t smem = (size_t)(ACH + 2) * TILE_BYTES + (size_t)4 * ACH * KV_TILE_BYTES + B_COUNT * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
         const cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel,
