@@ -9,25 +9,44 @@
 // (i, i + head_dim/2) rotate in float with a host-built cos/sin table, queries and keys are
 // rounded to bfloat16 once, scores / softmax / output accumulate in float.
 //
-// The splits of one (sequence, KV head) are the blocks of a thread-block cluster: each block
-// leaves its partial (max, sum, output) in its own shared memory and, after a cluster barrier,
-// the blocks share out the rows and read one another's partials through distributed shared
-// memory.  No scratch in global memory, no second kernel.  The block whose split holds the
-// newest position writes that token's key and value to the cache before it reads them.
+// The kernel is built around its latency chain, since a decode step gives it little else to
+// win: at batch 8 and 2,048 keys a block reads 64 KB.
+//  * Keys and values of earlier positions cannot change during the step, so a block starts
+//    streaming its piece of the context into shared memory (cp.async, two stages of 128 keys)
+//    as soon as it is resident, before it waits for the q|k|v projection in front of it.
+//  * After the wait one round of 16-byte loads fetches the queries (and the new key and value in
+//    the block that owns the newest position); they are rotated into a shared tile, the new row
+//    goes to the cache and straight into the staged keys.  Fragments come from ldmatrix.
+//  * The splits of one (sequence, KV head) are the blocks of a thread-block cluster.  Each block
+//    pushes its partial (max, sum, output) rows into the shared memory of the block that owns the
+//    row, one cluster barrier makes them visible, and the owner merges and writes the row.  No
+//    scratch in global memory, no second kernel, no barrier after the merge.
 #include "common.cuh"
 
 #if SKV_DTYPE == SKV_BF16
 
-#include <cooperative_groups.h>
-
-namespace cg = cooperative_groups;
-
 namespace skv {
 
 constexpr int FHD = SKV_HEAD_DIM;
-constexpr int FKSTEPS = FHD / 16, FOTILES = FHD / 8, FVWORDS = FHD / 16;
-constexpr int FWARPS = 8;
-constexpr int FPITCH = FHD + 2;
+constexpr int FKSTEPS = FHD / 16, FOTILES = FHD / 8;
+constexpr int FWARPS = 8, FTHREADS = FWARPS * 32;
+constexpr int FCHUNK = FWARPS * 16;                 // keys per stage: one group of 16 per warp
+constexpr int FSTAGES = 2;
+constexpr int FROW = FHD * 2 + 16;                  // bytes between staged rows: ldmatrix reads 8 rows without bank conflicts
+constexpr int FPIECES = FHD / 8;                    // 16-byte pieces per row
+constexpr int FSTAGE_BYTES = 2 * FCHUNK * FROW;     // keys, then values
+constexpr int FPITCH = FHD + 2;                     // floats per partial row: outputs, max, sum
+constexpr int FINBOX_ROWS = 24;                     // >= ceil(16 / blocks) * blocks for 1..8 blocks
+
+// shared memory, in bytes from the start
+constexpr int F_STAGES_AT = 0;                                      // also the warps' merge area after the loop
+constexpr int F_Q_AT = F_STAGES_AT + FSTAGES * FSTAGE_BYTES;        // [16][FROW] rotated queries
+constexpr int F_NEW_AT = F_Q_AT + 16 * FROW;                        // new key row, new value row
+constexpr int F_ANGLES_AT = F_NEW_AT + 2 * FROW;                    // [FHD/2] (cos, sin)
+constexpr int F_INBOX_AT = F_ANGLES_AT + (FHD / 2) * 8;             // [FINBOX_ROWS][FPITCH] floats, written by the cluster
+constexpr int F_SMEM_BYTES = F_INBOX_AT + FINBOX_ROWS * FPITCH * 4;
+static_assert(FWARPS * 16 * FPITCH * 4 <= FSTAGES * FSTAGE_BYTES, "the merge area reuses the stages");
+static_assert(F_SMEM_BYTES <= 227 * 1024, "shared memory");
 
 __device__ __forceinline__ void f_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                       uint32_t b0, uint32_t b1) {
@@ -36,6 +55,40 @@ __device__ __forceinline__ void f_mma(float (&c)[4], uint32_t a0, uint32_t a1, u
         "{%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void f_ldmatrix(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+
+__device__ __forceinline__ void f_ldmatrix_trans(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+
+// 16 bytes global -> shared, asynchronously; `bytes` 0 writes zeros instead
+__device__ __forceinline__ void f_copy16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void f_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void f_wait_copies() { asm volatile("cp.async.wait_group %0;\n" ::"n"(PENDING) : "memory"); }
+
+__device__ __forceinline__ void f_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void f_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ uint32_t f_cluster_rank() {
+    uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r)); return r;
+}
+__device__ __forceinline__ uint32_t f_cluster_size() {
+    uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r)); return r;
+}
+// the address, in the cluster's shared window, of `local` (a shared address of this block) in block `rank`
+__device__ __forceinline__ uint32_t f_remote(uint32_t local, uint32_t rank) {
+    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(local), "r"(rank)); return r;
+}
+__device__ __forceinline__ void f_remote_store(uint32_t address, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(address), "f"(v) : "memory");
 }
 
 __device__ __forceinline__ float f_exp2(float x) {
@@ -49,26 +102,17 @@ __device__ __forceinline__ uint32_t f_pack(float lo, float hi) {
     return *(const uint32_t*)&v;
 }
 
-// element d of a head after rotation; x points at the head's head_dim floats, angles at the
-// position's head_dim/2 (cos, sin) pairs (null: no rotation)
-__device__ __forceinline__ float rotated(const float* x, const float2* angles, int d) {
-    constexpr int HALF = FHD / 2;
-    if (!angles) return x[d];
-    if (d < HALF) { const float2 a = angles[d]; return x[d] * a.x - x[d + HALF] * a.y; }
-    const float2 a = angles[d - HALF];
-    return x[d - HALF] * a.y + x[d] * a.x;
-}
-
-__global__ void __launch_bounds__(FWARPS * 32, FHD <= 64 ? 2 : 1)
+__global__ void __launch_bounds__(FTHREADS, FHD <= 64 ? 2 : 1)
 decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __restrict__ cos_sin,
                               __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                               const int* __restrict__ block_table, int table_width,
                               const int* __restrict__ ctx_after, __nv_bfloat16* __restrict__ out, int num_heads,
                               int num_kv_heads, int block_size, float scale, int window, int splits, int m_tiles,
                               int write_kv) {
-    extern __shared__ float fused_smem[];             // [warps][16][FPITCH] merge area, then [16][FPITCH] result
-    float* result = fused_smem + (size_t)FWARPS * 16 * FPITCH;
+    extern __shared__ __align__(128) unsigned char fused_smem[];
+    constexpr int HALF = FHD / 2;
     pdl_launch_dependents();
+    f_cluster_arrive();                               // "this block is running": waited for before the first remote store
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tig = lane & 3;
     const int seq = blockIdx.x;
@@ -86,159 +130,211 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     const int per_split = (end_group - first_group + splits - 1) / splits;
     const int my_first = first_group + split * per_split;
     const int my_end = min(end_group, my_first + per_split);
+    const int n_chunks = my_end > my_first ? (my_end - my_first + FWARPS - 1) / FWARPS : 0;
     const int* table = block_table + (size_t)seq * table_width;
     const float scale_log2 = scale * 1.4426950408889634f;
     const float* token = qkv + (size_t)seq * (q_dim + 2 * kv_dim);
-    const float2* angles = cos_sin ? cos_sin + (size_t)pos * (FHD / 2) : nullptr;
-
-    // One group of 16 keys: the lane's share of its keys (for Q.K^T) and values (for P.V), in registers.
-    struct GroupData { uint2 kb[2][FKSTEPS]; uint32_t vw[4][FVWORDS]; };
-    auto load_group = [&](int group, GroupData& data) {
-        const int j0 = group << 4;
-        const int block = table[j0 / block_size];
-        const size_t base = ((size_t)(block * num_kv_heads + kv_head) * block_size + (j0 % block_size)) * FHD;
-        const __nv_bfloat16* k_rows = k_cache + base;
-        const __nv_bfloat16* v_rows = v_cache + base;
-        const int keys[4] = {2 * tig, 2 * tig + 1, 2 * tig + 8, 2 * tig + 9};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const bool live = j0 + keys[i] < ctx;
-            const uint32_t* src = (const uint32_t*)(v_rows + (size_t)keys[i] * FHD + g * (FHD / 8));
-#pragma unroll
-            for (int w = 0; w < FVWORDS; ++w) data.vw[i][w] = live ? src[w] : 0u;
-        }
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const bool live = j0 + 8 * t + g < ctx;
-            const __nv_bfloat16* key_row = k_rows + (size_t)(8 * t + g) * FHD + 4 * tig;
-#pragma unroll
-            for (int step = 0; step < FKSTEPS; ++step)
-                data.kb[t][step] = live ? *(const uint2*)(key_row + 16 * step) : make_uint2(0u, 0u);
-        }
-    };
-    // Keys and values of earlier positions were written by earlier steps, so the warp's first group can be
-    // fetched before waiting for the kernel in front (the q|k|v projection): the loads overlap its end.  Not
-    // the group that holds the new position, and not for a layer that reads a cache another layer of this
-    // same step writes (write_kv == 0).
     const int newest_group = pos >> 4;
-    const int first_mine = my_first + warp;
-    const bool prefetched = write_kv && first_mine < my_end && first_mine != newest_group;
-    GroupData ahead;
-    if (prefetched) load_group(first_mine, ahead);
+    const bool owns_newest = newest_group >= my_first && newest_group < my_end;
+
+    const uint32_t smem = smem_u32(fused_smem);
+    float2* angles = (float2*)(fused_smem + F_ANGLES_AT);
+    float* inbox = (float*)(fused_smem + F_INBOX_AT);
+
+    // Stage chunk c (groups my_first + 8c ...) of this block's keys and values.  Rows past the context are
+    // zero-filled: a masked key has weight 0, and 0 times whatever lay in shared memory need not be 0.
+    auto issue_chunk = [&](int c) {
+        if (c < n_chunks) {
+            const int key0 = (my_first + c * FWARPS) << 4;
+            const int key_end = min(ctx, my_end << 4);
+            const uint32_t stage = smem + F_STAGES_AT + (c % FSTAGES) * FSTAGE_BYTES;
+            for (int i = threadIdx.x; i < FCHUNK * FPIECES; i += FTHREADS) {
+                const int row = i / FPIECES, piece = i - row * FPIECES;
+                const int key = key0 + row;
+                const bool live = key < key_end;
+                size_t at = 0;
+                if (live) {
+                    const int block = table[key / block_size];
+                    at = ((size_t)(block * num_kv_heads + kv_head) * block_size + (key % block_size)) * FHD + piece * 8;
+                }
+                const uint32_t dst = stage + row * FROW + piece * 16;
+                f_copy16(dst, k_cache + at, live ? 16 : 0);
+                f_copy16(dst + FCHUNK * FROW, v_cache + at, live ? 16 : 0);
+            }
+        }
+        f_commit();
+    };
+    // Keys and values of earlier positions were written by earlier steps (and the one row that this step
+    // writes is replaced below), so the copies need not wait for the kernel in front.
+    issue_chunk(0);
+    issue_chunk(1);
+    // rotation angles of the new position come from a table that the step does not write
+    for (int i = threadIdx.x; i < HALF; i += FTHREADS)
+        angles[i] = cos_sin ? cos_sin[(size_t)pos * HALF + i] : make_float2(1.0f, 0.0f);
+    // query rows that no head fills stay zero
+    for (int i = threadIdx.x; i < 16 * FROW / 16; i += FTHREADS)
+        *(uint4*)(fused_smem + F_Q_AT + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
     pdl_wait();
 
-    // the block whose split holds the newest position puts that token's key and value in the cache
-    if (write_kv && newest_group >= my_first && newest_group < my_end) {
-        const int block = table[pos / block_size];
-        const size_t at = ((size_t)(block * num_kv_heads + kv_head) * block_size + (pos % block_size)) * FHD;
-        const float* k_new = token + q_dim + (size_t)kv_head * FHD;
-        const float* v_new = token + q_dim + kv_dim + (size_t)kv_head * FHD;
-        for (int d = threadIdx.x; d < FHD; d += blockDim.x) {
-            k_cache[at + d] = __float2bfloat16_rn(rotated(k_new, angles, d));
-            v_cache[at + d] = __float2bfloat16_rn(v_new[d]);
+    // Queries (and the new key, where this block owns the newest position and the layer writes its cache):
+    // item `rows` is the key.  One thread rotates four pairs (d, d + HALF).
+    {
+        const bool with_key = owns_newest && write_kv;
+        const int items = (rows + (with_key ? 1 : 0)) * (HALF / 4);
+        size_t new_at = 0;
+        if (owns_newest) {
+            const int block = table[pos / block_size];
+            new_at = ((size_t)(block * num_kv_heads + kv_head) * block_size + (pos % block_size)) * FHD;
         }
-        __threadfence_block();
+        for (int i = threadIdx.x; i < items; i += FTHREADS) {
+            const int item = i / (HALF / 4), quad = i - item * (HALF / 4);
+            const float* x = item < rows ? token + (size_t)(head0 + item) * FHD : token + q_dim + (size_t)kv_head * FHD;
+            const float4 a = *(const float4*)(x + 4 * quad), b = *(const float4*)(x + HALF + 4 * quad);
+            const float xa[4] = {a.x, a.y, a.z, a.w}, xb[4] = {b.x, b.y, b.z, b.w};
+            float first[4], second[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 cs = angles[4 * quad + e];
+                first[e] = xa[e] * cs.x - xb[e] * cs.y;          // as rotated() of elementwise.cu
+                second[e] = xa[e] * cs.y + xb[e] * cs.x;
+            }
+            const uint2 low = make_uint2(f_pack(first[0], first[1]), f_pack(first[2], first[3]));
+            const uint2 high = make_uint2(f_pack(second[0], second[1]), f_pack(second[2], second[3]));
+            unsigned char* row = item < rows ? fused_smem + F_Q_AT + item * FROW : fused_smem + F_NEW_AT;
+            *(uint2*)(row + 8 * quad) = low;
+            *(uint2*)(row + 2 * HALF + 8 * quad) = high;
+            if (item == rows) {
+                *(uint2*)(k_cache + new_at + 4 * quad) = low;
+                *(uint2*)(k_cache + new_at + HALF + 4 * quad) = high;
+            }
+        }
+        if (owns_newest) {
+            // the new value row (not rotated); or, for a layer that reads a cache which another layer of this
+            // step has written, that row and its key as they now stand in the cache
+            for (int i = threadIdx.x; i < (write_kv ? 1 : 2) * (FHD / 4); i += FTHREADS) {
+                const int which = write_kv ? 1 : i / (FHD / 4), quad = i % (FHD / 4);
+                uint2 packed;
+                if (write_kv) {
+                    const float4 v = *(const float4*)(token + q_dim + kv_dim + (size_t)kv_head * FHD + 4 * quad);
+                    packed = make_uint2(f_pack(v.x, v.y), f_pack(v.z, v.w));
+                    *(uint2*)(v_cache + new_at + 4 * quad) = packed;
+                } else {
+                    packed = *(const uint2*)((which ? v_cache : k_cache) + new_at + 4 * quad);
+                }
+                *(uint2*)(fused_smem + F_NEW_AT + which * FROW + 8 * quad) = packed;
+            }
+        }
     }
-    __syncthreads();                                  // the block's later loads of that row see the stores
+    __syncthreads();
 
-    // rotated query fragments: rows g and g+8 are heads head0+g, head0+g+8; elements 16s + 4tig .. +3
+    // query fragments: rows g and g+8 are heads head0+g, head0+g+8
     uint32_t qa[FKSTEPS][4];
 #pragma unroll
-    for (int s = 0; s < FKSTEPS; ++s) {
-        float top[4] = {0.0f, 0.0f, 0.0f, 0.0f}, bottom[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (g < rows) {
-            const float* x = token + (size_t)(head0 + g) * FHD;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) top[e] = rotated(x, angles, 16 * s + 4 * tig + e);
-        }
-        if (g + 8 < rows) {
-            const float* x = token + (size_t)(head0 + g + 8) * FHD;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) bottom[e] = rotated(x, angles, 16 * s + 4 * tig + e);
-        }
-        qa[s][0] = f_pack(top[0], top[1]); qa[s][1] = f_pack(bottom[0], bottom[1]);
-        qa[s][2] = f_pack(top[2], top[3]); qa[s][3] = f_pack(bottom[2], bottom[3]);
-    }
+    for (int s = 0; s < FKSTEPS; ++s)
+        f_ldmatrix(qa[s], smem + F_Q_AT + ((lane & 7) + ((lane >> 3) & 1) * 8) * FROW + (16 * s + (lane >> 4) * 8) * 2);
 
     float o[FOTILES][4];
 #pragma unroll
     for (int j = 0; j < FOTILES; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
 
-    for (int group = first_mine; group < my_end; group += FWARPS) {
-        const int j0 = group << 4;
-        GroupData data;
-        if (group == first_mine && prefetched) data = ahead;
-        else load_group(group, data);
-        float s[2][4];
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.0f;
-#pragma unroll
-            for (int step = 0; step < FKSTEPS; ++step)
-                f_mma(s[t], qa[step][0], qa[step][1], qa[step][2], qa[step][3], data.kb[t][step].x, data.kb[t][step].y);
+    for (int c = 0; c < n_chunks; ++c) {
+        f_wait_copies<1>();                           // chunk c has landed (this thread's part)
+        __syncthreads();                              // ... and everybody's
+        const int group0 = my_first + c * FWARPS;
+        const uint32_t stage = smem + F_STAGES_AT + (c % FSTAGES) * FSTAGE_BYTES;
+        if (owns_newest && newest_group >= group0 && newest_group < group0 + FWARPS) {
+            // the newest position's row, which the copy fetched as the cache had it before this step
+            const int row = pos - (group0 << 4);
+            unsigned char* base = fused_smem + F_STAGES_AT + (c % FSTAGES) * FSTAGE_BYTES;
+            for (int i = threadIdx.x; i < 2 * FPIECES; i += FTHREADS) {
+                const int which = i / FPIECES, piece = i - which * FPIECES;
+                *(uint4*)(base + which * FCHUNK * FROW + row * FROW + piece * 16) =
+                    *(const uint4*)(fused_smem + F_NEW_AT + which * FROW + piece * 16);
+            }
+            __syncthreads();
         }
-        float tile_max[2] = {-INFINITY, -INFINITY};
+        const int group = group0 + warp;
+        if (group < my_end) {
+            const int j0 = group << 4;
+            const uint32_t k_rows = stage + warp * 16 * FROW, v_rows = k_rows + FCHUNK * FROW;
+            float s[2][4];
+            s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
+            for (int step = 0; step < FKSTEPS; ++step) {
+                uint32_t kb[4];                       // keys 0-7: dims 0-7, 8-15 of the step; keys 8-15 likewise
+                f_ldmatrix(kb, k_rows + ((lane & 7) + (lane >> 4) * 8) * FROW + (16 * step + ((lane >> 3) & 1) * 8) * 2);
+                f_mma(s[0], qa[step][0], qa[step][1], qa[step][2], qa[step][3], kb[0], kb[1]);
+                f_mma(s[1], qa[step][0], qa[step][1], qa[step][2], qa[step][3], kb[2], kb[3]);
+            }
+            float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int key = j0 + 8 * t + 2 * tig + (c & 1);
-                const float v = (key < ctx && key >= lo) ? s[t][c] * scale_log2 : -INFINITY;
-                s[t][c] = v;
-                tile_max[c >> 1] = fmaxf(tile_max[c >> 1], v);
+            for (int t = 0; t < 2; ++t) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = j0 + 8 * t + 2 * tig + (e & 1);
+                    const float v = (key < ctx && key >= lo) ? s[t][e] * scale_log2 : -INFINITY;
+                    s[t][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                }
+            }
+            float corr[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float m = tile_max[r];
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                const float new_max = fmaxf(row_max[r], m);
+                corr[r] = new_max == -INFINITY ? 1.0f : f_exp2(row_max[r] - new_max);
+                row_max[r] = new_max;
+            }
+            float p[2][4];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float m = row_max[e >> 1];
+                    p[t][e] = m == -INFINITY ? 0.0f : f_exp2(s[t][e] - m);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+                row_sum[r] = row_sum[r] * corr[r] + p[0][2 * r] + p[0][2 * r + 1] + p[1][2 * r] + p[1][2 * r + 1];
+#pragma unroll
+            for (int j = 0; j < FOTILES; ++j) {
+                o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+            const uint32_t a0 = f_pack(p[0][0], p[0][1]), a1 = f_pack(p[0][2], p[0][3]);
+            const uint32_t a2 = f_pack(p[1][0], p[1][1]), a3 = f_pack(p[1][2], p[1][3]);
+#pragma unroll
+            for (int j = 0; j < FOTILES; j += 2) {
+                uint32_t vb[4];                       // dims 8j..: keys 0-7, 8-15; dims 8j+8..: keys 0-7, 8-15
+                f_ldmatrix_trans(vb, v_rows + ((lane & 7) + ((lane >> 3) & 1) * 8) * FROW + (8 * j + (lane >> 4) * 8) * 2);
+                f_mma(o[j], a0, a1, a2, a3, vb[0], vb[1]);
+                f_mma(o[j + 1], a0, a1, a2, a3, vb[2], vb[3]);
             }
         }
-        float corr[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            float m = tile_max[r];
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-            const float new_max = fmaxf(row_max[r], m);
-            corr[r] = new_max == -INFINITY ? 1.0f : f_exp2(row_max[r] - new_max);
-            row_max[r] = new_max;
-        }
-        float p[2][4];
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float m = row_max[c >> 1];
-                p[t][c] = m == -INFINITY ? 0.0f : f_exp2(s[t][c] - m);
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r)
-            row_sum[r] = row_sum[r] * corr[r] + p[0][2 * r] + p[0][2 * r + 1] + p[1][2 * r] + p[1][2 * r + 1];
-#pragma unroll
-        for (int j = 0; j < FOTILES; ++j) {
-            o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
-        }
-        const uint32_t a0 = f_pack(p[0][0], p[0][1]), a1 = f_pack(p[0][2], p[0][3]);
-        const uint32_t a2 = f_pack(p[1][0], p[1][1]), a3 = f_pack(p[1][2], p[1][3]);
-#pragma unroll
-        for (int w = 0; w < FVWORDS; ++w) {
-            f_mma(o[2 * w], a0, a1, a2, a3, __byte_perm(data.vw[0][w], data.vw[1][w], 0x5410),
-                  __byte_perm(data.vw[2][w], data.vw[3][w], 0x5410));
-            f_mma(o[2 * w + 1], a0, a1, a2, a3, __byte_perm(data.vw[0][w], data.vw[1][w], 0x7632),
-                  __byte_perm(data.vw[2][w], data.vw[3][w], 0x7632));
-        }
+        __syncthreads();                              // the stage is free
+        issue_chunk(c + FSTAGES);
     }
-    // merge the warps into `result`: rows x (head_dim outputs, max, sum)
+    f_wait_copies<0>();
+    __syncthreads();
+
+    // the warps' partial rows (outputs, max, sum), in what were the stages
+    float* partial = (float*)(fused_smem + F_STAGES_AT);
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
         row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
     }
-    float* mine = fused_smem + (size_t)warp * 16 * FPITCH;
+    float* mine = partial + (size_t)warp * 16 * FPITCH;
 #pragma unroll
     for (int j = 0; j < FOTILES; ++j) {
-        const int d0 = (2 * tig) * (FHD / 8) + j, d1 = (2 * tig + 1) * (FHD / 8) + j;
-        mine[g * FPITCH + d0] = o[j][0];
-        mine[g * FPITCH + d1] = o[j][1];
-        mine[(g + 8) * FPITCH + d0] = o[j][2];
-        mine[(g + 8) * FPITCH + d1] = o[j][3];
+        mine[g * FPITCH + 8 * j + 2 * tig] = o[j][0];
+        mine[g * FPITCH + 8 * j + 2 * tig + 1] = o[j][1];
+        mine[(g + 8) * FPITCH + 8 * j + 2 * tig] = o[j][2];
+        mine[(g + 8) * FPITCH + 8 * j + 2 * tig + 1] = o[j][3];
     }
     if (tig == 0) {
         mine[g * FPITCH + FHD] = row_max[0];
@@ -247,55 +343,50 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
         mine[(g + 8) * FPITCH + FHD + 1] = row_sum[1];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < 16 * FPITCH; idx += blockDim.x) {
+    f_cluster_wait();                                 // every block of the cluster runs: its shared memory may be written
+
+    // Merge the warps, and push each row to the block that owns it: row r belongs to block r % blocks and
+    // lands in that block's inbox at [(r / blocks) * blocks + this block's rank].
+    const int rank = (int)f_cluster_rank(), blocks = (int)f_cluster_size();
+    const uint32_t inbox_local = smem + F_INBOX_AT;
+    for (int idx = threadIdx.x; idx < rows * FPITCH; idx += FTHREADS) {
         const int r = idx / FPITCH, d = idx - r * FPITCH;
         float m = -INFINITY;
-        for (int w = 0; w < FWARPS; ++w) m = fmaxf(m, fused_smem[((size_t)w * 16 + r) * FPITCH + FHD]);
-        float value;
-        if (d == FHD) {
-            value = m;
-        } else {
-            float total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < FWARPS; ++w) m = fmaxf(m, partial[((size_t)w * 16 + r) * FPITCH + FHD]);
+        float value = m;
+        if (d != FHD) {
+            value = 0.0f;
             if (m != -INFINITY) {
+#pragma unroll
                 for (int w = 0; w < FWARPS; ++w) {
-                    const float* tile = fused_smem + ((size_t)w * 16 + r) * FPITCH;
-                    total += f_exp2(tile[FHD] - m) * tile[d];      // column FHD+1 (the sums) is weighted the same way
+                    const float* tile = partial + ((size_t)w * 16 + r) * FPITCH;
+                    value += f_exp2(tile[FHD] - m) * tile[d];      // column FHD+1 (the sums) is weighted the same way
                 }
             }
-            value = total;
         }
-        result[idx] = value;
+        const int slot = (r / blocks) * blocks + rank;
+        f_remote_store(f_remote(inbox_local + (slot * FPITCH + d) * 4, (uint32_t)(r % blocks)), value);
     }
-    if (splits == 1) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < rows * FHD; idx += blockDim.x) {
-            const int r = idx / FHD, d = idx - r * FHD;
-            out[((size_t)seq * num_heads + head0 + r) * FHD + d] =
-                __float2bfloat16_rn(result[r * FPITCH + d] / result[r * FPITCH + FHD + 1]);
-        }
-        return;
-    }
-    // merge the splits: the cluster's blocks share out the rows and read every block's `result`
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    const int rank = (int)cluster.block_rank(), blocks = (int)cluster.num_blocks();
-    for (int idx = threadIdx.x; idx < rows * FHD; idx += blockDim.x) {
-        const int r = idx / FHD, d = idx - r * FHD;
-        if (r % blocks != rank) continue;
+    f_cluster_arrive();
+    f_cluster_wait();                                 // the pushes are visible; nobody reads another block from here on
+
+    for (int idx = threadIdx.x; idx < ((rows - rank + blocks - 1) / blocks) * FHD; idx += FTHREADS) {
+        const int mine_index = idx / FHD, d = idx - mine_index * FHD;
+        const int r = mine_index * blocks + rank;
+        const float* slots = inbox + (size_t)mine_index * blocks * FPITCH;
         float m = -INFINITY;
-        for (int b = 0; b < blocks; ++b) m = fmaxf(m, cluster.map_shared_rank(result, b)[r * FPITCH + FHD]);
+        for (int b = 0; b < blocks; ++b) m = fmaxf(m, slots[b * FPITCH + FHD]);
         float total = 0.0f, sum = 0.0f;
         for (int b = 0; b < blocks; ++b) {
-            const float* remote = cluster.map_shared_rank(result, b);
-            const float mb = remote[r * FPITCH + FHD];
+            const float mb = slots[b * FPITCH + FHD];
             if (mb == -INFINITY) continue;
             const float weight = f_exp2(mb - m);
-            total += weight * remote[r * FPITCH + d];
-            sum += weight * remote[r * FPITCH + FHD + 1];
+            total += weight * slots[b * FPITCH + d];
+            sum += weight * slots[b * FPITCH + FHD + 1];
         }
         out[((size_t)seq * num_heads + head0 + r) * FHD + d] = __float2bfloat16_rn(total / sum);
     }
-    cluster.sync();                                   // nobody leaves while its shared memory is being read
 }
 
 }  // namespace skv
@@ -321,7 +412,7 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
         return fail("skv_attention_decode_fused", "operands must be 16-byte aligned");
     const int group_size = num_heads / num_kv_heads;
     const int m_tiles = (group_size + 15) / 16;
-    const size_t smem = (size_t)(FWARPS + 1) * 16 * FPITCH * sizeof(float);
+    const size_t smem = F_SMEM_BYTES;
     static bool configured = false;
     if (!configured) {
         const cudaError_t status = cudaFuncSetAttribute(decode_attention_fused_kernel,
@@ -331,7 +422,7 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
     }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(n_seqs, num_kv_heads * m_tiles, splits);
-    config.blockDim = dim3(FWARPS * 32);
+    config.blockDim = dim3(FTHREADS);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
     cudaLaunchAttribute attributes[2];

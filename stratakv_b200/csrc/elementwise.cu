@@ -13,21 +13,35 @@ namespace skv {
 // ---------------------------------------------------------------------------
 // x[t, :] = table[ids[t], :] widened to float.  An id outside the vocabulary
 // (hosts check before launching) writes zeros and raises the flag.
+// With `row_scale` the factor 1 / sqrt(mean(row^2) + eps_next) is left at row_scale[t] and the row
+// times `gamma_next` at scaled[t, :], for the projection after the first norm (see linear.cu).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int hidden, int vocab, int* __restrict__ flag) {
+                             float* __restrict__ out, int hidden, int vocab, int* __restrict__ flag,
+                             float* __restrict__ row_scale, const float* __restrict__ gamma_next, float eps_next,
+                             T* __restrict__ scaled) {
+    __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* row_out = out + (size_t)t * hidden;
-    if (id < 0 || id >= vocab) {
-        for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_out[c] = 0.0f;
-        if (threadIdx.x == 0 && flag) atomicOr(flag, 1);
-        return;
+    const bool bad = id < 0 || id >= vocab;
+    if (bad && threadIdx.x == 0 && flag) atomicOr(flag, 1);
+    const T* row = table + (size_t)(bad ? 0 : id) * hidden;
+    float partial = 0.0f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = bad ? 0.0f : to_float(row[c]);
+        row_out[c] = v;
+        if (row_scale) {
+            partial = fmaf(v, v, partial);
+            scaled[(size_t)t * hidden + c] = from_float<T>(v * gamma_next[c]);
+        }
     }
-    const T* row = table + (size_t)id * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) row_out[c] = to_float(row[c]);
+    if (row_scale) {
+        const float total = block_sum(partial, scratch);
+        if (threadIdx.x == 0) row_scale[t] = 1.0f / sqrtf(total / (float)hidden + eps_next);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -222,12 +236,14 @@ SKV_EXPORT int skv_library_dtype() { return SKV_DTYPE; }
 SKV_EXPORT int skv_library_head_dim() { return SKV_HEAD_DIM; }
 
 SKV_EXPORT int skv_embed(const void* table, const int* ids, float* out, int n_tokens, int hidden,
-                         int vocab, int* flag, cudaStream_t stream) {
+                         int vocab, int* flag, float* row_scale, void* scaled, const float* gamma_next,
+                         float eps_next, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) return fail("skv_embed", "hidden and vocab must be positive");
     const int threads = hidden >= 1024 ? 256 : 128;
     return launch_pdl("skv_embed", embed_kernel<skv_t>, dim3(n_tokens), dim3(threads), 0, stream,
-                      (const skv_t*)table, ids, out, hidden, vocab, flag);
+                      (const skv_t*)table, ids, out, hidden, vocab, flag, row_scale, gamma_next, eps_next,
+                      (skv_t*)scaled);
 }
 
 SKV_EXPORT int skv_rmsnorm(const float* x, const float* gamma, float eps, void* out, const int* rows,

@@ -108,9 +108,13 @@ linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void
     }
 }
 
+struct NormArgs { const float* row_scale; const int* rows; float* partials; int partial_stride; unsigned int* counter;
+                  const float* gamma_next; float eps_next; void* scaled_out; float* row_scale_out; };
+
 static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                         int* flag, cudaStream_t stream) {
+                         int* flag, const NormArgs& norm, cudaStream_t stream) {
     (void)flag;
+    if (norm.row_scale || norm.partials) return fail("skv_linear(float)", "the norm-fused form exists in the bfloat16 build only");
     dim3 grid((N + FBN - 1) / FBN, (M + FBM - 1) / FBM);
     return launch_pdl("skv_linear(float)", linear_f32_kernel, grid, dim3(256), 0, stream, (const float*)a,
                       (const float*)w, out, M, N, K, mode, act);
@@ -132,6 +136,28 @@ __device__ __forceinline__ uint4 load_weight16(const uint4* p) {
     return STREAM ? __ldcs(p) : __ldg(p);
 }
 
+// RMSNorm folded into the projections around it.  The kernel that updates the float residual stream
+// (residual-add mode) also leaves, per token, the updated row times the NEXT norm's weight in bfloat16
+// and the factor 1 / sqrt(mean(row^2) + eps); the projection after that norm takes those activations
+// and multiplies its result by the factor, which is one number per token and so commutes with the
+// product.  Everything about the norm stays in float; the activations are rounded to bfloat16 once, as
+// they are when the norm runs as a kernel of its own.
+// A row's sum of squares is made in a fixed order whatever the timing: every block leaves the sum
+// over its 16 columns, and the block that finishes last (a counter tells it) adds them up in order.
+struct NormArgs {
+    // consumer side (null row_scale: plain projection)
+    const float* row_scale;        // [rows] factor of each row of X
+    const int* rows;               // token m reads row rows[m] of X and of row_scale (null: row m)
+    // producer side, residual-add mode (null partials: not wanted)
+    float* partials;               // scratch [M, partial_stride], partial_stride >= blocks of the grid
+    int partial_stride;
+    unsigned int* counter;         // zero before the launch; the kernel leaves it zero
+    const float* gamma_next;       // [N] weight of the norm that reads the stream next
+    float eps_next;
+    __nv_bfloat16* scaled_out;     // [M, N] = bfloat16(updated out * gamma_next)
+    float* row_scale_out;          // [M] = 1 / sqrt(mean(updated out[m, :]^2) + eps_next)
+};
+
 // One block owns 16 rows of W and one chunk of 8*TG tokens.  Its warps take the
 // 32-wide k steps round robin, then their partial tiles are summed in shared
 // memory in warp order (a fixed order: results do not depend on timing).
@@ -140,7 +166,7 @@ __device__ __forceinline__ uint4 load_weight16(const uint4* p) {
 template <int TG, int U, bool STREAM, int MAX_WARPS>
 __global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS == 4 ? (TG == 1 ? 5 : (TG == 2 ? 4 : 2)) : (MAX_WARPS == 8 && TG <= 2 ? 2 : 1))
 skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
-                          void* __restrict__ out, int M, int N, int K, int mode, int act) {
+                          void* __restrict__ out, int M, int N, int K, int mode, int act, const NormArgs norm) {
     extern __shared__ float red[];                 // [warps][16][8*TG + 1]
     constexpr int COLS = 8 * TG, PITCH = COLS + 1;
     pdl_launch_dependents();
@@ -175,7 +201,12 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
     for (int t = 0; t < TG; ++t) {
         const int m = m0 + t * 8 + g;
         has_x[t] = m < M;
-        x_ptr[t] = X + (size_t)min(m, M - 1) * K + tig * 8;
+        const int safe = min(m, M - 1);
+        x_ptr[t] = X + (size_t)(norm.rows ? norm.rows[safe] : safe) * K + tig * 8;
+    }
+    if (norm.row_scale && !norm.rows && threadIdx.x * 32 < M) {
+        // the factors are wanted after the main loop: bring their lines close meanwhile
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(norm.row_scale + threadIdx.x * 32));
     }
     float acc[TG][4];
 #pragma unroll
@@ -208,6 +239,7 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
         const int r = idx & 15, m = idx >> 4;
         float sum = 0.0f;
         for (int w = 0; w < warps; ++w) sum += red[((size_t)w * 16 + r) * PITCH + m];
+        if (norm.row_scale && m0 + m < M) sum *= norm.row_scale[norm.rows ? norm.rows[m0 + m] : m0 + m];
         red[(size_t)r * PITCH + m] = sum;          // warp 0's tile becomes the total
         // (each (r, m) is read and written by this thread only)
     }
@@ -222,6 +254,39 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
                 ((__nv_bfloat16*)out)[(size_t)gm * half_n + o] = __float2bfloat16_rn(activate(gate, act) * up);
             }
         }
+    } else if (mode == MODE_ADD_F32 && norm.partials) {
+        // residual sum; the updated row times the next norm's weight; its sum of squares over this block's columns
+        for (int idx = threadIdx.x; idx < 16 * COLS; idx += blockDim.x) {        // whole warps stay together
+            const int r = idx & 15, m = idx >> 4;
+            float updated = 0.0f;
+            if (m0 + m < M && n0 + r < N) {
+                float* at = (float*)out + (size_t)(m0 + m) * N + n0 + r;
+                updated = *at + red[(size_t)r * PITCH + m];
+                *at = updated;
+                norm.scaled_out[(size_t)(m0 + m) * N + n0 + r] = __float2bfloat16_rn(updated * norm.gamma_next[n0 + r]);
+            }
+            float square = updated * updated;
+#pragma unroll
+            for (int offset = 8; offset > 0; offset >>= 1) square += __shfl_xor_sync(0xffffffffu, square, offset);
+            if (r == 0 && m0 + m < M) norm.partials[(size_t)(m0 + m) * norm.partial_stride + blockIdx.x] = square;
+        }
+        // the last block to get here adds the partial sums up (the grid has one chunk of tokens: M <= 8*TG)
+        __shared__ bool last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) last = atomicAdd(norm.counter, 1u) == gridDim.x - 1;
+        __syncthreads();
+        if (last) {
+            __threadfence();
+            for (int m = warp; m < M; m += warps) {
+                const float* partial = norm.partials + (size_t)m * norm.partial_stride;
+                float total = 0.0f;
+                for (int p = lane; p < (int)gridDim.x; p += 32) total += __ldcg(partial + p);
+                total = warp_sum(total);
+                if (lane == 0) norm.row_scale_out[m] = 1.0f / sqrtf(total / (float)N + norm.eps_next);
+            }
+            if (threadIdx.x == 0) *norm.counter = 0u;
+        }
     } else {
         for (int idx = threadIdx.x; idx < 16 * COLS; idx += blockDim.x) {
             const int r = idx & 15, m = idx >> 4;
@@ -232,17 +297,17 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
 
 template <int TG, int U, int MAX_WARPS>
 static int launch_skinny_as(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                            int warps, cudaStream_t stream) {
+                            int warps, const NormArgs& norm, cudaStream_t stream) {
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
     const size_t smem = (size_t)warps * 16 * (8 * TG + 1) * sizeof(float);
     dim3 grid(row_tiles, chunks);
     if (chunks == 1)
         return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, true, MAX_WARPS>, grid,
                           dim3(warps * 32), smem, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N,
-                          K, mode, act);
+                          K, mode, act, norm);
     return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, false, MAX_WARPS>, grid,
                       dim3(warps * 32), smem, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)a, out, M, N, K,
-                      mode, act);
+                      mode, act, norm);
 }
 
 // Warps per block.  Many row tiles (>= 4 per SM): 4 warps, compiled to fit 5 blocks on an SM so that
@@ -251,7 +316,7 @@ static int launch_skinny_as(const void* a, const void* w, void* out, int M, int 
 // would need more than two rounds of loads each.  Never more warps than k steps.
 template <int TG, int U, int MAX_WARPS>
 static int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                         cudaStream_t stream) {
+                         const NormArgs& norm, cudaStream_t stream) {
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
     const int steps = (K + 31) / 32;
     const long long blocks = (long long)row_tiles * chunks;
@@ -259,9 +324,9 @@ static int launch_skinny(const void* a, const void* w, void* out, int M, int N, 
     if (warps == 8 && MAX_WARPS >= 16 && steps > 8 * U * 2) warps = 16;
     if (warps > MAX_WARPS) warps = MAX_WARPS;
     while (warps > 1 && warps > steps) warps >>= 1;
-    if (warps <= 4) return launch_skinny_as<TG, U, 4>(a, w, out, M, N, K, mode, act, warps, stream);
-    if (warps <= 8 || MAX_WARPS < 16) return launch_skinny_as<TG, U, 8>(a, w, out, M, N, K, mode, act, warps, stream);
-    return launch_skinny_as<TG, U, 16>(a, w, out, M, N, K, mode, act, warps, stream);
+    if (warps <= 4) return launch_skinny_as<TG, U, 4>(a, w, out, M, N, K, mode, act, warps, norm, stream);
+    if (warps <= 8 || MAX_WARPS < 16) return launch_skinny_as<TG, U, 8>(a, w, out, M, N, K, mode, act, warps, norm, stream);
+    return launch_skinny_as<TG, U, 16>(a, w, out, M, N, K, mode, act, warps, norm, stream);
 }
 
 // gemm_tcgen05.cu: the tensor-memory GEMM that serves steps with many tokens
@@ -277,18 +342,20 @@ static bool tcgen05_enabled() {
 }
 
 static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                         int* flag, cudaStream_t stream) {
+                         int* flag, const NormArgs& norm, cudaStream_t stream) {
     if (K % 8 != 0)
         return fail("skv_linear(bfloat16)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15)
         return fail("skv_linear(bfloat16)", "operands must be 16-byte aligned");
+    if ((norm.row_scale || norm.partials) && M > 64)
+        return fail("skv_linear(bfloat16)", "the norm-fused form serves steps of at most 64 tokens");
     if (M > 64 && tcgen05_enabled()) return linear_tcgen05(a, w, out, M, N, K, mode, flag, stream);
     // at most 8 warps and under 100 registers a thread: two blocks fit on an SM, so the next
     // kernel's weight loads are in flight while this one finishes
-    if (M <= 8) return launch_skinny<1, 8, 16>(a, w, out, M, N, K, mode, act, stream);
-    if (M <= 16) return launch_skinny<2, 8, 16>(a, w, out, M, N, K, mode, act, stream);
-    if (M <= 32) return launch_skinny<4, 4, 8>(a, w, out, M, N, K, mode, act, stream);
-    return launch_skinny<8, 4, 8>(a, w, out, M, N, K, mode, act, stream);
+    if (M <= 8) return launch_skinny<1, 8, 16>(a, w, out, M, N, K, mode, act, norm, stream);
+    if (M <= 16) return launch_skinny<2, 8, 16>(a, w, out, M, N, K, mode, act, norm, stream);
+    if (M <= 32) return launch_skinny<4, 4, 8>(a, w, out, M, N, K, mode, act, norm, stream);
+    return launch_skinny<8, 4, 8>(a, w, out, M, N, K, mode, act, norm, stream);
 }
 #endif
 
@@ -296,14 +363,50 @@ static int launch_linear(const void* a, const void* w, void* out, int M, int N, 
 
 using namespace skv;
 
-// `flag` (may be null): bit 2 (value 4) is raised if a pipeline wait inside a kernel timed out.
-SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                          int* flag, cudaStream_t stream) {
-    if (M <= 0) return 0;
+static int check_linear(int M, int N, int K, int mode, int act) {
     if (N <= 0 || K <= 0) return fail("skv_linear", "N and K must be positive");
     if (mode < 0 || mode > 3) return fail("skv_linear", "unknown epilogue mode");
     if (mode == MODE_GATED && N % 16 != 0)
         return fail("skv_linear", "a gated weight must have a multiple of 16 rows (gate/up tiles of 8)");
     if (act != ACT_SILU) return fail("skv_linear", "unknown activation");
-    return launch_linear(a, w, out, M, N, K, mode, act, flag, stream);
+    (void)M;
+    return 0;
+}
+
+// `flag` (may be null): bit 2 (value 4) is raised if a pipeline wait inside a kernel timed out.
+// With `row_scale_out` (residual-add mode, at most 64 tokens, bfloat16 build) the kernel also leaves what the
+// projection after the next norm needs (see NormArgs); `partials` is scratch of [M, partial_stride] floats with
+// partial_stride >= N/16 rounded up, `counter` one zeroed word that the kernel leaves zeroed.
+SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+                          int* flag, float* row_scale_out, void* scaled_out, const float* gamma_next, float eps_next,
+                          float* partials, int partial_stride, unsigned int* counter, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (int code = check_linear(M, N, K, mode, act)) return code;
+    NormArgs norm = {};
+    if (row_scale_out) {
+        if (mode != MODE_ADD_F32) return fail("skv_linear", "a norm is folded into the residual-add mode only");
+        if (!gamma_next || !scaled_out || !partials || !counter || partial_stride < (N + 15) / 16)
+            return fail("skv_linear", "the next norm's weight, a place for the scaled rows, scratch for N/16 partial sums per token and a counter are needed");
+        norm.partials = partials;
+        norm.partial_stride = partial_stride;
+        norm.counter = counter;
+        norm.gamma_next = gamma_next;
+        norm.eps_next = eps_next;
+        norm.scaled_out = (decltype(norm.scaled_out))scaled_out;
+        norm.row_scale_out = row_scale_out;
+    }
+    return launch_linear(a, w, out, M, N, K, mode, act, flag, norm, stream);
+}
+
+// The projection after a folded norm: `a` holds rows of (stream * norm weight) in bfloat16, token m reads
+// row rows[m] (or m), and the result is multiplied by row_scale[that row].  bfloat16 build, at most 64 tokens.
+SKV_EXPORT int skv_linear_normed(const void* a, const float* row_scale, const int* rows, const void* w, void* out,
+                                 int M, int N, int K, int mode, int act, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (int code = check_linear(M, N, K, mode, act)) return code;
+    if (!row_scale) return fail("skv_linear_normed", "the rows' factors are needed");
+    NormArgs norm = {};
+    norm.row_scale = row_scale;
+    norm.rows = rows;
+    return launch_linear(a, w, out, M, N, K, mode, act, nullptr, norm, stream);
 }

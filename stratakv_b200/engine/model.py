@@ -17,6 +17,7 @@ from ..parts.base import CacheRequest, Runtime, StepBatch, TensorRequest
 from ..parts.block import Layer
 from ..parts.registry import part_class
 from ..parts.spec import ModelSpec
+from ..residual import MAX_FUSED_ROWS, ResidualStats
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorRequest]:
@@ -127,12 +128,25 @@ class Model:
         rt, spec = self.rt, self.spec
         ops = rt.kernels()
         x = rt.workspace.get("residual", (step.n_tokens, spec.hidden_size), torch.float32)
-        ops.embed(self.embedding, step.token_ids, x, self.flags)
-        for entry in spec.schedule:
+        stats = None
+        if step.is_decode and rt.dtype == torch.bfloat16 and step.n_tokens <= MAX_FUSED_ROWS:
+            # few rows: norms are folded into the projections after them (residual.py)
+            stats = ResidualStats.allocate(rt.workspace.get, step.n_tokens, spec.hidden_size, rt.dtype)
+        step.residual_stats = stats
+        final = self.final_norm if self.final_norm.folds_norm else None
+        readers = [self.layers[entry.layer].first_norm for entry in spec.schedule] + [final]
+        if stats is not None:
+            stats.expect(readers[0])
+        ops.embed(self.embedding, step.token_ids, x, self.flags, stats=stats)
+        for index, entry in enumerate(spec.schedule):
+            step.norm_after_layer = readers[index + 1]
             self.layers[entry.layer].forward(step, x, entry)
         if n_want == 0:
             return None
-        y = self.final_norm.forward(x, rows=want_rows, name="final_normed")
+        if stats is not None and self.final_norm.folds_norm:
+            y = self.final_norm.forward(x, rows=want_rows, name="final_normed", stats=stats)
+        else:
+            y = self.final_norm.forward(x, rows=want_rows, name="final_normed")
         logits = rt.workspace.get("logits", (n_want, spec.vocab_size), torch.float32)
         ops.linear(y, self.head, logits, _ops.MODE_STORE_F32)
         return logits

@@ -12,6 +12,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from .csrc.build import BuildError, build_library
+from .residual import COLUMNS_PER_PARTIAL, MAX_FUSED_ROWS, NormedRows
 
 MODE_STORE, MODE_STORE_F32, MODE_ADD_F32, MODE_GATED = 0, 1, 2, 3
 ACTIVATIONS = {"silu": 0, "swish": 0}
@@ -26,6 +27,8 @@ def _ptr(tensor: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
 
 
+_NULL = ctypes.c_void_p(0)
+_NO_FOLD = (_NULL, _NULL, _NULL, ctypes.c_float(0.0), _NULL, 0, _NULL)
 _SCOPED_STREAM = None
 
 
@@ -91,16 +94,35 @@ class Kernels:
             raise KernelError(f"{name} must be contiguous")
 
     # ---- kernels -------------------------------------------------------------
-    def embed(self, table, ids, out, flag=None):
-        """out[t, :] = table[ids[t], :] as float32."""
+    def embed(self, table, ids, out, flag=None, stats=None):
+        """out[t, :] = table[ids[t], :] as float32; with ``stats`` each row's sum of squares too."""
         self._want(table, self.dtype, "table"); self._want(ids, torch.int32, "ids")
         self._want(out, torch.float32, "out")
         n, hidden = out.shape
         vocab = table.shape[0]
         if table.shape[1] != hidden or ids.numel() != n:
             raise KernelError("embed: shapes do not agree")
-        self._check(self.lib.skv_embed(_ptr(table), _ptr(ids), _ptr(out), n, hidden, vocab, _ptr(flag), _stream()),
-                    "embed")
+        fold = self._fold_target(stats, n, hidden)
+        self._check(self.lib.skv_embed(_ptr(table), _ptr(ids), _ptr(out), n, hidden, vocab, _ptr(flag),
+                                       *(fold[:4] if fold else _NO_FOLD[:4]), _stream()), "embed")
+        if stats is not None:
+            stats.filled() if fold else stats.invalidate()
+
+    def _fold_target(self, stats, rows: int, width: int):
+        """Arguments (rows' factors, scaled rows, next norm's weight and eps, scratch for partial sums, its
+        stride, counter) for a kernel that writes ``rows`` rows of the stream; None where it cannot fold."""
+        if stats is None or stats.next_norm is None or self.dtype != torch.bfloat16 or rows > MAX_FUSED_ROWS:
+            return None
+        gamma = stats.next_norm.gamma
+        self._want(gamma, torch.float32, "gamma"); self._want(stats.partials, torch.float32, "partials")
+        self._want(stats.scaled, self.dtype, "scaled"); self._want(stats.row_scale, torch.float32, "row_scale")
+        self._want(stats.counter, torch.int32, "counter")
+        if (gamma.numel() != width or tuple(stats.scaled.shape) != (rows, width) or stats.row_scale.numel() != rows
+                or stats.partials.shape[0] != rows
+                or stats.partials.shape[1] * COLUMNS_PER_PARTIAL < width):
+            raise KernelError("the buffers of the folded norm do not match the stream")
+        return (_ptr(stats.row_scale), _ptr(stats.scaled), _ptr(gamma), ctypes.c_float(stats.next_norm.spec.eps),
+                _ptr(stats.partials), stats.partials.shape[1], _ptr(stats.counter))
 
     def rmsnorm(self, x, gamma, eps: float, out, rows=None):
         """out[r, :] = rmsnorm(x[rows[r] or r, :]) * gamma, in the compute dtype."""
@@ -119,9 +141,22 @@ class Kernels:
         self._check(self.lib.skv_rmsnorm(_ptr(x), _ptr(gamma), ctypes.c_float(eps), _ptr(out), _ptr(rows),
                                          n_rows, hidden, _stream()), "rmsnorm")
 
-    def linear(self, a, w, out, mode: int = MODE_STORE, activation: str = "silu", flag=None):
-        """out = a[M,K] . w[N,K]^T with the epilogue ``mode``."""
-        self._want(a, self.dtype, "a"); self._want(w, self.dtype, "w")
+    def linear(self, a, w, out, mode: int = MODE_STORE, activation: str = "silu", flag=None, stats=None):
+        """out = a[M,K] . w[N,K]^T with the epilogue ``mode``.
+
+        ``a`` may be ``residual.NormedRows``: the norm is applied while the activations are
+        loaded.  ``stats`` (residual-add mode): the statistics of ``out`` are brought up to date where
+        the kernel can do that, and marked unknown where it cannot."""
+        normed = a if isinstance(a, NormedRows) else None
+        if normed is None:
+            self._want(a, self.dtype, "a")
+        else:
+            self._want(normed.scaled, self.dtype, "scaled"); self._want(normed.row_scale, torch.float32, "row_scale")
+            if normed.rows is not None:
+                self._want(normed.rows, torch.int32, "rows")
+            if normed.row_scale.numel() != normed.scaled.shape[0]:
+                raise KernelError("linear: one factor per row of the normalised input is needed")
+        self._want(w, self.dtype, "w")
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K:
@@ -133,8 +168,24 @@ class Kernels:
             raise KernelError(f"linear: out must be [{M}, {out_cols}], got {list(out.shape)}")
         if activation not in ACTIVATIONS:
             raise KernelError(f"linear: unknown activation '{activation}'")
+        if stats is not None and mode != MODE_ADD_F32:
+            raise KernelError("linear: statistics are kept by the residual-add mode only")
+        if normed is not None:
+            if stats is not None:
+                raise KernelError("linear: a folded norm on the input and statistics of the output do not go together")
+            self._check(self.lib.skv_linear_normed(
+                _ptr(normed.scaled), _ptr(normed.row_scale), _ptr(normed.rows), _ptr(w), _ptr(out), M, N, K, mode,
+                ACTIVATIONS[activation], _stream()), "linear")
+            return
+        fold = self._fold_target(stats, M, N)
         self._check(self.lib.skv_linear(_ptr(a), _ptr(w), _ptr(out), M, N, K, mode, ACTIVATIONS[activation],
-                                        _ptr(flag if flag is not None else self.error_flag), _stream()), "linear")
+                                        _ptr(flag if flag is not None else self.error_flag), *(fold or _NO_FOLD), _stream()),
+                    "linear")
+        if stats is not None:
+            if fold:
+                stats.filled()
+            else:
+                stats.invalidate()
 
     def rope_kv_write(self, qkv, cos_sin, positions, token_seq, block_table, q_out, k_cache, v_cache,
                       num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, write_kv: bool):

@@ -28,6 +28,7 @@ def decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148
 
 class PagedAttention(Mixer):
     graph_safe = True
+    folds_norm = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -81,7 +82,7 @@ class PagedAttention(Mixer):
             ops.attention_decode_fused(qkv, self.position.fusion_table(step.max_ctx), k_cache, v_cache, table,
                                        step.ctx_after, ctx, s.num_heads, s.num_kv_heads, s.head_dim,
                                        step.cache.block_size, s.scale, s.window, splits, writes_cache)
-            ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32)
+            ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
             return
         q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
         self.position.rotate_and_store(step, qkv, q, k_cache, v_cache, table, s.num_heads, s.num_kv_heads,
@@ -104,7 +105,7 @@ class PagedAttention(Mixer):
         else:
             ops.attention(q, k_cache, v_cache, table, step.positions, step.token_seq, ctx, s.num_heads,
                           s.num_kv_heads, s.head_dim, step.cache.block_size, s.scale, s.window)
-        ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32)
+        ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
 
 
 register_mixer("attention", PagedAttention)

@@ -90,6 +90,8 @@ class StepBatch:
     block_tables: Dict[int, torch.Tensor]
     cache: Any                         # cache.KVCache
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)
+    residual_stats: Any = None         # residual.ResidualStats when norms may be folded into projections
+    norm_after_layer: Any = None       # then: the foldable norm that reads the stream after the running layer
 
     @property
     def is_decode(self) -> bool:
@@ -101,6 +103,10 @@ class Part:
     # True if forward() only launches kernels on fixed device buffers (no host reads of
     # device data, no host-side per-sequence work), so a step can be captured in a CUDA graph.
     graph_safe = False
+    # True if the part (a norm) can hand over ``residual.NormedRows`` instead of applying itself, or
+    # (a mixer, a feed-forward) takes them as its input and keeps ``step.residual_stats`` up to date
+    # when it adds to the stream.  The arrangement asks before it uses either.
+    folds_norm = False
 
     def __init__(self, spec, runtime: Runtime):
         self.spec = spec

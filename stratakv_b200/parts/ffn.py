@@ -31,6 +31,7 @@ def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 class GatedMlp(FeedForward):
     graph_safe = True
+    folds_norm = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -63,7 +64,7 @@ class GatedMlp(FeedForward):
         ops = rt.kernels()
         z = rt.workspace.get("ffn_hidden", (h.shape[0], self.padded), rt.dtype)
         ops.linear(h, self.w_gate_up, z, _ops.MODE_GATED, s.activation)
-        ops.linear(z, self.w_down, x, _ops.MODE_ADD_F32)
+        ops.linear(z, self.w_down, x, _ops.MODE_ADD_F32, stats=getattr(step, "residual_stats", None))
 
 
 register_ffn("gated_mlp", GatedMlp)

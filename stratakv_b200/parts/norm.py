@@ -9,10 +9,12 @@ import torch
 
 from .base import Norm, TensorRequest
 from .registry import register_norm
+from ..residual import NormedRows
 
 
 class RMSNorm(Norm):
     graph_safe = True
+    folds_norm = True
 
     @classmethod
     def expected_tensors(cls, spec):
@@ -21,7 +23,10 @@ class RMSNorm(Norm):
     def bind(self, tensors):
         self.gamma = self.rt.upload(tensors[self.spec.weight], torch.float32)
 
-    def forward(self, x, rows=None, out=None, name="normed"):
+    def forward(self, x, rows=None, out=None, name="normed", stats=None):
+        """``stats`` prepared for this norm: leave the rest of the work to the consumer's projection."""
+        if stats is not None and out is None and stats.ready_for(self):
+            return NormedRows(stats.scaled, stats.row_scale, rows)
         n_rows = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = self.rt.workspace.get(name, (n_rows, self.spec.size), self.rt.dtype)

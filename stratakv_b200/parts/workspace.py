@@ -14,7 +14,8 @@ class Workspace:
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self.generation = 0          # bumped whenever a buffer is reallocated
 
-    def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, shape, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """``zero``: the buffer is zero when it is first handed out (and after it had to grow)."""
         count = 1
         for d in shape:
             count *= int(d)
@@ -24,7 +25,7 @@ class Workspace:
             capacity = max(count, 1)
             if buffer is not None:
                 capacity = max(capacity, 2 * buffer.numel())
-            buffer = torch.empty(capacity, dtype=dtype, device=self.device)
+            buffer = (torch.zeros if zero else torch.empty)(capacity, dtype=dtype, device=self.device)
             self._buffers[key] = buffer
             self.generation += 1
         return buffer[:count].view(*shape)

@@ -1,0 +1,75 @@
+"""Bookkeeping that lets a norm be folded into the projections around it.
+
+At decode the float residual stream is a few rows; an RMSNorm kernel of its own
+costs a launch and a round trip through memory for almost no work.  RMSNorm is
+``x * weight`` times one factor per row, ``1 / sqrt(mean(x^2) + eps)``, and a
+factor per row commutes with the projection that follows.  So the kernel that
+writes the stream (the embedding, a residual-add projection) also leaves, in a
+``ResidualStats``, each row times the weight of the norm that reads the stream
+next (in the compute dtype) and the row's factor; that norm then hands over
+``NormedRows`` instead of running, and its consumer's first projection
+multiplies its result by the factor.  All of the norm's arithmetic stays in
+float32 and the activations are rounded once, as with the separate kernel; only
+the place of that rounding (before the factor instead of after it) differs.
+
+Who does what: the model and the arrangement call ``expect(norm)`` before a part
+that may write the stream, naming the norm that reads it next (None: nobody who
+can use it).  The writing kernel's wrapper fills the buffers and calls
+``filled()``, or ``invalidate()`` where it cannot.  A norm asks ``ready_for(self)``.
+A norm that folds has ``gamma`` (float32 weight) and ``spec.eps``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Optional
+
+import torch
+
+MAX_FUSED_ROWS = 64        # the small-batch projection kernel serves at most this many tokens
+COLUMNS_PER_PARTIAL = 16   # a residual-add projection sums squares over 16 columns per block
+
+
+class ResidualStats:
+    """``scaled[row]`` is the stream's row times ``prepared_for.gamma`` and ``row_scale[row]``
+    that norm's factor for the row, while ``prepared_for`` is not None."""
+
+    def __init__(self, scaled: torch.Tensor, row_scale: torch.Tensor, partials: torch.Tensor, counter: torch.Tensor):
+        self.scaled = scaled
+        self.row_scale = row_scale
+        self.partials = partials       # scratch of the writing kernel: [rows, >= width / 16]
+        self.counter = counter         # one int32, zero between kernels
+        self.next_norm: Any = None
+        self.prepared_for: Any = None
+
+    @classmethod
+    def allocate(cls, get, rows: int, width: int, dtype):
+        """Buffers from ``get(name, shape, dtype, zero=False)`` (a workspace's)."""
+        partial_width = (width + COLUMNS_PER_PARTIAL - 1) // COLUMNS_PER_PARTIAL
+        return cls(get("residual_scaled", (rows, width), dtype), get("residual_row_scale", (rows,), torch.float32),
+                   get("residual_partials", (rows, partial_width), torch.float32),
+                   get("residual_counter", (1,), torch.int32, zero=True))
+
+    def expect(self, norm) -> None:
+        self.next_norm = norm
+
+    def filled(self) -> None:
+        self.prepared_for = self.next_norm
+
+    def invalidate(self) -> None:
+        self.prepared_for = None
+
+    def ready_for(self, norm) -> bool:
+        return norm is not None and self.prepared_for is norm
+
+
+@dataclass
+class NormedRows:
+    """A norm not yet finished: ``scaled[rows]`` still lacks the factor per row, ``row_scale[rows]``,
+    which the consuming projection applies to its result."""
+    scaled: torch.Tensor
+    row_scale: torch.Tensor
+    rows: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return (self.scaled.shape[0] if self.rows is None else self.rows.numel(), self.scaled.shape[1])

@@ -18,7 +18,7 @@ class DoubleKernels:
         self.head_dim = head_dim
         self.calls = []
 
-    def embed(self, table, ids, out, flag=None):
+    def embed(self, table, ids, out, flag=None, stats=None):
         self.calls.append("embed")
         out.copy_(table[ids.long()].float())
 
@@ -28,7 +28,7 @@ class DoubleKernels:
         inv = 1.0 / torch.sqrt((src * src).mean(dim=-1, keepdim=True) + eps)
         out.copy_((src * inv * gamma).to(out.dtype))
 
-    def linear(self, a, w, out, mode=MODE_STORE, activation="silu"):
+    def linear(self, a, w, out, mode=MODE_STORE, activation="silu", flag=None, stats=None):
         self.calls.append("linear")
         result = a.float() @ w.float().T
         if mode == MODE_GATED:

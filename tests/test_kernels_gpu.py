@@ -107,6 +107,129 @@ def test_linear_gated(dtype, M, F, K):
         close(out, ref, dtype)
 
 
+class _Norm:
+    """Stands for a norm part: all the kernels want of it is its weight and eps."""
+    def __init__(self, gamma, eps):
+        from types import SimpleNamespace
+        self.gamma, self.spec = gamma, SimpleNamespace(eps=eps)
+
+
+def _stats(rows, width, dtype=torch.bfloat16, spare=0):
+    from stratakv_b200.residual import ResidualStats
+    nan = lambda *shape: torch.full(shape, float("nan"), device="cuda")
+    return ResidualStats(nan(rows, width).to(dtype), nan(rows), nan(rows, (width + 15) // 16 + spare),
+                         torch.zeros(1, device="cuda", dtype=torch.int32))
+
+
+def _folded(stats, norm, rows=None):
+    from stratakv_b200.residual import NormedRows
+    assert stats.ready_for(norm)
+    return NormedRows(stats.scaled, stats.row_scale, rows)
+
+
+@pytest.mark.parametrize("M,N,K,hidden_out", [(1, 176, 64, 72), (5, 104, 80, 40), (8, 2560, 2048, 2048),
+                                              (16, 96, 1024, 1000), (33, 48, 96, 104), (64, 256, 4096, 512)])
+def test_linear_with_folded_norm(M, N, K, hidden_out):
+    """RMSNorm folded into the projections around it: the kernel that writes the stream (the embedding,
+    a residual-add projection) leaves the row times the norm's weight and the row's factor, the
+    projection after the norm applies the factor; together they are the norm, then the projection
+    (src/layers/rmsnorm.cpp:63-97)."""
+    from stratakv_b200 import ops
+    dtype = torch.bfloat16
+    k = lib(dtype)
+    norm_a = _Norm((1 + 0.2 * torch.randn(K, device="cuda")).float(), 3e-5)
+    norm_b = _Norm((1 + 0.2 * torch.randn(K, device="cuda")).float(), 2e-6)
+    w = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(dtype)
+    rows = torch.randperm(M, device="cuda").to(torch.int32)[: max(1, M // 2)]
+    x = torch.empty(M, K, device="cuda")
+    stats = _stats(M, K, spare=3)
+
+    def check(norm):
+        eps = norm.spec.eps
+        factor = torch.rsqrt((x.double() ** 2).mean(-1) + eps)
+        assert torch.allclose(stats.row_scale.double(), factor, rtol=1e-5, atol=0)
+        assert torch.equal(stats.scaled, (x * norm.gamma).to(dtype))
+        assert int(stats.counter) == 0
+        for selected in (None, rows):
+            m = M if selected is None else selected.numel()
+            fused = torch.full((m, N), float("nan"), device="cuda")
+            k.linear(_folded(stats, norm, selected), w, fused, ops.MODE_STORE_F32)
+            xs = x.double() if selected is None else x.double()[selected.long()]
+            exact_h = xs * torch.rsqrt((xs ** 2).mean(-1, keepdim=True) + eps) * norm.gamma.double()
+            ref = exact_h @ w.double().T
+            # the activations are rounded to bfloat16 once (half a unit in the last of 8 bits)
+            bound = 2.0 ** -8 * (exact_h.abs() @ w.double().abs().T) + 1e-5
+            assert ((fused.double() - ref).abs() <= bound).all()
+            h = torch.empty(m, K, device="cuda", dtype=dtype)
+            k.rmsnorm(x, norm.gamma, eps, h, selected)
+            separate = torch.empty(m, N, device="cuda")
+            k.linear(h, w, separate, ops.MODE_STORE_F32)
+            assert ((fused - separate).abs().double() <= bound).all()
+
+    # 1. the stream from the embedding
+    vocab = 37
+    table = torch.randn(vocab, K, device="cuda").to(dtype)
+    ids = torch.randint(0, vocab, (M,), device="cuda", dtype=torch.int32)
+    stats.expect(norm_a)
+    k.embed(table, ids, x, stats=stats)
+    assert stats.ready_for(norm_a) and not stats.ready_for(norm_b)
+    assert torch.equal(x, table[ids.long()].float())
+    check(norm_a)
+    # 2. the stream after a residual-add projection, twice (the counter must come back to zero)
+    for _ in range(2):
+        a = torch.randn(M, hidden_out, device="cuda").to(dtype)
+        w_add = (torch.randn(K, hidden_out, device="cuda") / math.sqrt(hidden_out)).to(dtype)
+        plain = x.clone()
+        k.linear(a, w_add, plain, ops.MODE_ADD_F32)
+        stats.expect(norm_b)
+        k.linear(a, w_add, x, ops.MODE_ADD_F32, stats=stats)
+        assert torch.equal(x, plain)                                     # the sum itself is unchanged
+        assert stats.ready_for(norm_b)
+        check(norm_b)
+    # 3. a gated projection takes the folded norm too
+    F = 64
+    w_gu = (torch.randn(2 * F, K, device="cuda") / math.sqrt(K)).to(dtype)
+    z = torch.empty(M, F, device="cuda", dtype=dtype)
+    k.linear(_folded(stats, norm_b), pack_gate_up(w_gu), z, ops.MODE_GATED, "silu")
+    xs = x.double()
+    exact_h = xs * torch.rsqrt((xs ** 2).mean(-1, keepdim=True) + norm_b.spec.eps) * norm_b.gamma.double()
+    gate, up = exact_h @ w_gu[:F].double().T, exact_h @ w_gu[F:].double().T
+    ref = gate * torch.sigmoid(gate) * up
+    # the activations' rounding moves gate and up by at most 2^-8 sum |h||w| each (silu has slope <= 1.1),
+    # and the result is rounded to bfloat16
+    err_gate = 2.0 ** -8 * (exact_h.abs() @ w_gu[:F].double().abs().T)
+    err_up = 2.0 ** -8 * (exact_h.abs() @ w_gu[F:].double().abs().T)
+    allowed = 1.1 * err_gate * (up.abs() + err_up) + (gate * torch.sigmoid(gate)).abs() * err_up + 2.0 ** -8 * ref.abs() + 1e-6
+    assert ((z.double() - ref).abs() <= allowed).all()
+    # 4. nobody to read the statistics: the kernel leaves none
+    stats.expect(None)
+    k.linear(a, w_add, x, ops.MODE_ADD_F32, stats=stats)
+    assert not stats.ready_for(norm_b)
+
+
+def test_folded_norm_refusals():
+    from stratakv_b200 import ops
+    from stratakv_b200.ops import KernelError
+    from stratakv_b200.residual import NormedRows
+    k = lib(torch.bfloat16)
+    x = torch.zeros(80, 64, device="cuda")
+    stats = _stats(80, 64)
+    w = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match="one factor per row"):
+        k.linear(NormedRows(stats.scaled, stats.row_scale[:5]), w, torch.zeros(80, 32, device="cuda"),
+                 ops.MODE_STORE_F32)
+    with pytest.raises(KernelError, match="at most 64 tokens"):
+        k.linear(NormedRows(stats.scaled, stats.row_scale), w, torch.zeros(80, 32, device="cuda"),
+                 ops.MODE_STORE_F32)
+    # more rows than the kernel folds a norm for: the sum is made, nothing is left for the norm
+    norm = _Norm(torch.ones(64, device="cuda"), 1e-5)
+    stats.expect(norm)
+    stats.filled()
+    a = torch.zeros(80, 32, device="cuda", dtype=torch.bfloat16)
+    k.linear(a, torch.zeros(64, 32, device="cuda", dtype=torch.bfloat16), x, ops.MODE_ADD_F32, stats=stats)
+    assert not stats.ready_for(norm)
+
+
 def test_linear_refuses_bad_sizes():
     from stratakv_b200 import ops
     from stratakv_b200.ops import KernelError
