@@ -23,6 +23,7 @@
 //    scratch in global memory, no second kernel, no barrier after the merge.
 #include "common.cuh"
 
+
 #if SKV_DTYPE == SKV_BF16
 
 namespace skv {
@@ -31,7 +32,7 @@ constexpr int FHD = SKV_HEAD_DIM;
 constexpr int FKSTEPS = FHD / 16, FOTILES = FHD / 8;
 constexpr int FWARPS = 8, FTHREADS = FWARPS * 32;
 constexpr int FCHUNK = FWARPS * 16;                 // keys per stage: one group of 16 per warp
-constexpr int FSTAGES = 2;
+constexpr int FSTAGES = 2;                          // deeper staging measured slower: it costs the second block of an SM
 constexpr int FROW = FHD * 2 + 16;                  // bytes between staged rows: ldmatrix reads 8 rows without bank conflicts
 constexpr int FPIECES = FHD / 8;                    // 16-byte pieces per row
 constexpr int FSTAGE_BYTES = 2 * FCHUNK * FROW;     // keys, then values
@@ -39,14 +40,15 @@ constexpr int FPITCH = FHD + 2;                     // floats per partial row: o
 constexpr int FINBOX_ROWS = 24;                     // >= ceil(16 / blocks) * blocks for 1..8 blocks
 
 // shared memory, in bytes from the start
-constexpr int F_STAGES_AT = 0;                                      // also the warps' merge area after the loop
-constexpr int F_Q_AT = F_STAGES_AT + FSTAGES * FSTAGE_BYTES;        // [16][FROW] rotated queries
+constexpr int F_Q_AT = 0;                                           // [16][FROW] rotated queries
 constexpr int F_NEW_AT = F_Q_AT + 16 * FROW;                        // new key row, new value row
 constexpr int F_ANGLES_AT = F_NEW_AT + 2 * FROW;                    // [FHD/2] (cos, sin)
 constexpr int F_INBOX_AT = F_ANGLES_AT + (FHD / 2) * 8;             // [FINBOX_ROWS][FPITCH] floats, written by the cluster
-constexpr int F_SMEM_BYTES = F_INBOX_AT + FINBOX_ROWS * FPITCH * 4;
-static_assert(FWARPS * 16 * FPITCH * 4 <= FSTAGES * FSTAGE_BYTES, "the merge area reuses the stages");
-static_assert(F_SMEM_BYTES <= 227 * 1024, "shared memory");
+constexpr int F_STAGES_AT = (F_INBOX_AT + FINBOX_ROWS * FPITCH * 4 + 127) / 128 * 128;   // also the warps' merge area after the loop
+constexpr int F_SMEM_LIMIT = 227 * 1024;
+static_assert(FWARPS * 16 * FPITCH * 4 <= 2 * FSTAGE_BYTES, "the merge area reuses the stages");
+constexpr int F_SMEM_BYTES = F_STAGES_AT + FSTAGES * FSTAGE_BYTES;
+static_assert(F_SMEM_BYTES <= F_SMEM_LIMIT, "shared memory");
 
 __device__ __forceinline__ void f_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                       uint32_t b0, uint32_t b1) {
@@ -166,8 +168,8 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     };
     // Keys and values of earlier positions were written by earlier steps (and the one row that this step
     // writes is replaced below), so the copies need not wait for the kernel in front.
-    issue_chunk(0);
-    issue_chunk(1);
+#pragma unroll
+    for (int c = 0; c < FSTAGES; ++c) issue_chunk(c);
     // rotation angles of the new position come from a table that the step does not write
     for (int i = threadIdx.x; i < HALF; i += FTHREADS)
         angles[i] = cos_sin ? cos_sin[(size_t)pos * HALF + i] : make_float2(1.0f, 0.0f);
@@ -240,7 +242,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
 
     for (int c = 0; c < n_chunks; ++c) {
-        f_wait_copies<1>();                           // chunk c has landed (this thread's part)
+        f_wait_copies<FSTAGES - 1>();                 // chunk c has landed (this thread's part)
         __syncthreads();                              // ... and everybody's
         const int group0 = my_first + c * FWARPS;
         const uint32_t stage = smem + F_STAGES_AT + (c % FSTAGES) * FSTAGE_BYTES;

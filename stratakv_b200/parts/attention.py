@@ -26,6 +26,16 @@ def decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148
     return max(1, min(by_length, by_count, 64))
 
 
+def fused_decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148) -> int:
+    """The same for the fused kernel, whose pieces are the blocks of one cluster: the largest
+    power of two (other cluster sizes measured slower), at most 8, that keeps the grid within
+    two blocks per SM."""
+    by_length = max(1, max_ctx // 128)
+    by_count = 2 * sms // max(1, n_seqs * blocks_per_seq)
+    wanted = max(1, min(by_length, by_count, 8))
+    return 1 << (wanted.bit_length() - 1)
+
+
 class PagedAttention(Mixer):
     graph_safe = True
     folds_norm = True
@@ -78,7 +88,7 @@ class PagedAttention(Mixer):
         blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
         if step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table"):
             # one kernel: rotation, cache write, attention over the context in up to 8 pieces, merge
-            splits = min(8, decode_splits(n, blocks_per_seq, step.max_ctx))
+            splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx)
             ops.attention_decode_fused(qkv, self.position.fusion_table(step.max_ctx), k_cache, v_cache, table,
                                        step.ctx_after, ctx, s.num_heads, s.num_kv_heads, s.head_dim,
                                        step.cache.block_size, s.scale, s.window, splits, writes_cache)
