@@ -44,7 +44,9 @@ constexpr int F_Q_AT = 0;                                           // [16][FROW
 constexpr int F_NEW_AT = F_Q_AT + 16 * FROW;                        // new key row, new value row
 constexpr int F_ANGLES_AT = F_NEW_AT + 2 * FROW;                    // [FHD/2] (cos, sin)
 constexpr int F_INBOX_AT = F_ANGLES_AT + (FHD / 2) * 8;             // [FINBOX_ROWS][FPITCH] floats, written by the cluster
-constexpr int F_STAGES_AT = (F_INBOX_AT + FINBOX_ROWS * FPITCH * 4 + 127) / 128 * 128;   // also the warps' merge area after the loop
+constexpr int FTABLE = 512;                                         // entries of the block table kept in shared memory
+constexpr int F_TABLE_AT = F_INBOX_AT + FINBOX_ROWS * FPITCH * 4;   // [FTABLE] ints
+constexpr int F_STAGES_AT = (F_TABLE_AT + FTABLE * 4 + 127) / 128 * 128;   // also the warps' merge area after the loop
 constexpr int F_SMEM_LIMIT = 227 * 1024;
 static_assert(FWARPS * 16 * FPITCH * 4 <= 2 * FSTAGE_BYTES, "the merge area reuses the stages");
 constexpr int F_SMEM_BYTES = F_STAGES_AT + FSTAGES * FSTAGE_BYTES;
@@ -110,7 +112,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                               const int* __restrict__ block_table, int table_width,
                               const int* __restrict__ ctx_after, __nv_bfloat16* __restrict__ out, int num_heads,
                               int num_kv_heads, int block_size, float scale, int window, int splits, int m_tiles,
-                              int write_kv) {
+                              int write_kv, int block_shift) {
     extern __shared__ __align__(128) unsigned char fused_smem[];
     constexpr int HALF = FHD / 2;
     pdl_launch_dependents();
@@ -125,6 +127,11 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     const int rows = min(16, group_size - m_tile * 16);
     const int q_dim = num_heads * FHD, kv_dim = num_kv_heads * FHD;
 
+    // The block table's row goes to shared memory while the context length is on its way, so that the
+    // copies below start after one round trip to memory, not two.
+    const int* table = block_table + (size_t)seq * table_width;
+    int* table_near = (int*)(fused_smem + F_TABLE_AT);
+    for (int i = threadIdx.x; i < min(table_width, FTABLE); i += FTHREADS) table_near[i] = table[i];
     const int ctx = ctx_after[seq];
     const int pos = ctx - 1;                          // the new token's position
     const int lo = window > 0 ? max(0, ctx - window) : 0;
@@ -133,7 +140,6 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     const int my_first = first_group + split * per_split;
     const int my_end = min(end_group, my_first + per_split);
     const int n_chunks = my_end > my_first ? (my_end - my_first + FWARPS - 1) / FWARPS : 0;
-    const int* table = block_table + (size_t)seq * table_width;
     const float scale_log2 = scale * 1.4426950408889634f;
     const float* token = qkv + (size_t)seq * (q_dim + 2 * kv_dim);
     const int newest_group = pos >> 4;
@@ -142,6 +148,16 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     const uint32_t smem = smem_u32(fused_smem);
     float2* angles = (float2*)(fused_smem + F_ANGLES_AT);
     float* inbox = (float*)(fused_smem + F_INBOX_AT);
+    // rotation angles of the new position come from a table that the step does not write
+    static_assert(FHD / 2 <= FTHREADS, "one angle per thread");
+    float2 my_angle = make_float2(1.0f, 0.0f);
+    if (cos_sin && threadIdx.x < HALF) my_angle = cos_sin[(size_t)pos * HALF + threadIdx.x];
+    __syncthreads();                                  // the table is in shared memory
+    auto block_of = [&](int key) {
+        const int index = block_shift >= 0 ? key >> block_shift : key / block_size;
+        return index < FTABLE ? table_near[index] : table[index];
+    };
+    auto row_in_block = [&](int key) { return block_shift >= 0 ? key & (block_size - 1) : key % block_size; };
 
     // Stage chunk c (groups my_first + 8c ...) of this block's keys and values.  Rows past the context are
     // zero-filled: a masked key has weight 0, and 0 times whatever lay in shared memory need not be 0.
@@ -155,10 +171,8 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                 const int key = key0 + row;
                 const bool live = key < key_end;
                 size_t at = 0;
-                if (live) {
-                    const int block = table[key / block_size];
-                    at = ((size_t)(block * num_kv_heads + kv_head) * block_size + (key % block_size)) * FHD + piece * 8;
-                }
+                if (live)
+                    at = ((size_t)(block_of(key) * num_kv_heads + kv_head) * block_size + row_in_block(key)) * FHD + piece * 8;
                 const uint32_t dst = stage + row * FROW + piece * 16;
                 f_copy16(dst, k_cache + at, live ? 16 : 0);
                 f_copy16(dst + FCHUNK * FROW, v_cache + at, live ? 16 : 0);
@@ -170,9 +184,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     // writes is replaced below), so the copies need not wait for the kernel in front.
 #pragma unroll
     for (int c = 0; c < FSTAGES; ++c) issue_chunk(c);
-    // rotation angles of the new position come from a table that the step does not write
-    for (int i = threadIdx.x; i < HALF; i += FTHREADS)
-        angles[i] = cos_sin ? cos_sin[(size_t)pos * HALF + i] : make_float2(1.0f, 0.0f);
+    if (threadIdx.x < HALF) angles[threadIdx.x] = my_angle;
     // query rows that no head fills stay zero
     for (int i = threadIdx.x; i < 16 * FROW / 16; i += FTHREADS)
         *(uint4*)(fused_smem + F_Q_AT + i * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -185,10 +197,8 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
         const bool with_key = owns_newest && write_kv;
         const int items = (rows + (with_key ? 1 : 0)) * (HALF / 4);
         size_t new_at = 0;
-        if (owns_newest) {
-            const int block = table[pos / block_size];
-            new_at = ((size_t)(block * num_kv_heads + kv_head) * block_size + (pos % block_size)) * FHD;
-        }
+        if (owns_newest)
+            new_at = ((size_t)(block_of(pos) * num_kv_heads + kv_head) * block_size + row_in_block(pos)) * FHD;
         for (int i = threadIdx.x; i < items; i += FTHREADS) {
             const int item = i / (HALF / 4), quad = i - item * (HALF / 4);
             const float* x = item < rows ? token + (size_t)(head0 + item) * FHD : token + q_dim + (size_t)kv_head * FHD;
@@ -414,6 +424,9 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
         return fail("skv_attention_decode_fused", "operands must be 16-byte aligned");
     const int group_size = num_heads / num_kv_heads;
     const int m_tiles = (group_size + 15) / 16;
+    int block_shift = -1;                             // log2 of block_size where it is a power of two
+    for (int bit = 4; bit < 31; ++bit)
+        if (block_size == (1 << bit)) block_shift = bit;
     const size_t smem = F_SMEM_BYTES;
     static bool configured = false;
     if (!configured) {
@@ -439,7 +452,7 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
     const cudaError_t status = cudaLaunchKernelEx(
         &config, decode_attention_fused_kernel, qkv, (const float2*)cos_sin, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, block_table, table_width, ctx_after, (__nv_bfloat16*)out, num_heads, num_kv_heads,
-        block_size, scale, window, splits, m_tiles, write_kv);
+        block_size, scale, window, splits, m_tiles, write_kv, block_shift);
     if (status != cudaSuccess) return fail("skv_attention_decode_fused", cudaGetErrorString(status));
     return 0;
 }
