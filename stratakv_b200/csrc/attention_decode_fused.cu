@@ -32,7 +32,7 @@ constexpr int FHD = SKV_HEAD_DIM;
 constexpr int FKSTEPS = FHD / 16, FOTILES = FHD / 8;
 constexpr int FWARPS = 8, FTHREADS = FWARPS * 32;
 constexpr int FCHUNK = FWARPS * 16;                 // keys per stage: one group of 16 per warp
-constexpr int FSTAGES = 2;                          // deeper staging measured slower: it costs the second block of an SM
+constexpr int FMAX_STAGES = 4;                      // stages per launch: 2 .. FMAX_STAGES (see the launch below)
 constexpr int FROW = FHD * 2 + 16;                  // bytes between staged rows: ldmatrix reads 8 rows without bank conflicts
 constexpr int FPIECES = FHD / 8;                    // 16-byte pieces per row
 constexpr int FSTAGE_BYTES = 2 * FCHUNK * FROW;     // keys, then values
@@ -49,8 +49,7 @@ constexpr int F_TABLE_AT = F_INBOX_AT + FINBOX_ROWS * FPITCH * 4;   // [FTABLE] 
 constexpr int F_STAGES_AT = (F_TABLE_AT + FTABLE * 4 + 127) / 128 * 128;   // also the warps' merge area after the loop
 constexpr int F_SMEM_LIMIT = 227 * 1024;
 static_assert(FWARPS * 16 * FPITCH * 4 <= 2 * FSTAGE_BYTES, "the merge area reuses the stages");
-constexpr int F_SMEM_BYTES = F_STAGES_AT + FSTAGES * FSTAGE_BYTES;
-static_assert(F_SMEM_BYTES <= F_SMEM_LIMIT, "shared memory");
+static_assert(F_STAGES_AT + 2 * FSTAGE_BYTES <= F_SMEM_LIMIT, "shared memory");
 
 __device__ __forceinline__ void f_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                       uint32_t b0, uint32_t b1) {
@@ -112,7 +111,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                               const int* __restrict__ block_table, int table_width,
                               const int* __restrict__ ctx_after, __nv_bfloat16* __restrict__ out, int num_heads,
                               int num_kv_heads, int block_size, float scale, int window, int splits, int m_tiles,
-                              int write_kv, int block_shift) {
+                              int write_kv, int block_shift, int stages) {
     extern __shared__ __align__(128) unsigned char fused_smem[];
     constexpr int HALF = FHD / 2;
     pdl_launch_dependents();
@@ -165,7 +164,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
         if (c < n_chunks) {
             const int key0 = (my_first + c * FWARPS) << 4;
             const int key_end = min(ctx, my_end << 4);
-            const uint32_t stage = smem + F_STAGES_AT + (c % FSTAGES) * FSTAGE_BYTES;
+            const uint32_t stage = smem + F_STAGES_AT + (c % stages) * FSTAGE_BYTES;
             for (int i = threadIdx.x; i < FCHUNK * FPIECES; i += FTHREADS) {
                 const int row = i / FPIECES, piece = i - row * FPIECES;
                 const int key = key0 + row;
@@ -182,8 +181,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     };
     // Keys and values of earlier positions were written by earlier steps (and the one row that this step
     // writes is replaced below), so the copies need not wait for the kernel in front.
-#pragma unroll
-    for (int c = 0; c < FSTAGES; ++c) issue_chunk(c);
+    for (int c = 0; c < stages; ++c) issue_chunk(c);
     if (threadIdx.x < HALF) angles[threadIdx.x] = my_angle;
     // query rows that no head fills stay zero
     for (int i = threadIdx.x; i < 16 * FROW / 16; i += FTHREADS)
@@ -252,14 +250,17 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
 
     for (int c = 0; c < n_chunks; ++c) {
-        f_wait_copies<FSTAGES - 1>();                 // chunk c has landed (this thread's part)
+        // chunk c has landed (this thread's part) once all but the stages - 1 groups committed after it are complete
+        if (stages == 2) f_wait_copies<1>();
+        else if (stages == 3) f_wait_copies<2>();
+        else f_wait_copies<3>();
         __syncthreads();                              // ... and everybody's
         const int group0 = my_first + c * FWARPS;
-        const uint32_t stage = smem + F_STAGES_AT + (c % FSTAGES) * FSTAGE_BYTES;
+        const uint32_t stage = smem + F_STAGES_AT + (c % stages) * FSTAGE_BYTES;
         if (owns_newest && newest_group >= group0 && newest_group < group0 + FWARPS) {
             // the newest position's row, which the copy fetched as the cache had it before this step
             const int row = pos - (group0 << 4);
-            unsigned char* base = fused_smem + F_STAGES_AT + (c % FSTAGES) * FSTAGE_BYTES;
+            unsigned char* base = fused_smem + F_STAGES_AT + (c % stages) * FSTAGE_BYTES;
             for (int i = threadIdx.x; i < 2 * FPIECES; i += FTHREADS) {
                 const int which = i / FPIECES, piece = i - which * FPIECES;
                 *(uint4*)(base + which * FCHUNK * FROW + row * FROW + piece * 16) =
@@ -328,7 +329,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
             }
         }
         __syncthreads();                              // the stage is free
-        issue_chunk(c + FSTAGES);
+        issue_chunk(c + stages);
     }
     f_wait_copies<0>();
     __syncthreads();
@@ -427,14 +428,26 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
     int block_shift = -1;                             // log2 of block_size where it is a power of two
     for (int bit = 4; bit < 31; ++bit)
         if (block_size == (1 << bit)) block_shift = bit;
-    const size_t smem = F_SMEM_BYTES;
-    static bool configured = false;
-    if (!configured) {
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0, count = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+            return fail("skv_attention_decode_fused", "cannot read the number of SMs");
         const cudaError_t status = cudaFuncSetAttribute(decode_attention_fused_kernel,
-                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM_LIMIT);
         if (status != cudaSuccess) return fail("skv_attention_decode_fused", cudaGetErrorString(status));
-        configured = true;
+        sm_count = count;
     }
+    // Two stages of 128 keys let two blocks share an SM.  A block that has an SM to itself, and whose piece of
+    // the longest context is at most four stages, fetches the whole piece ahead instead (measured: batch 8 at
+    // 2,048 keys gains 3 % that way, while deeper staging of longer pieces loses 10 %).
+    const long long blocks = (long long)n_seqs * num_kv_heads * m_tiles * splits;
+    const long long piece_chunks = ((long long)table_width * block_size / splits + FCHUNK - 1) / FCHUNK;
+    const int room = (F_SMEM_LIMIT - F_STAGES_AT) / FSTAGE_BYTES;
+    int stages = 2;
+    if (blocks <= sm_count && piece_chunks <= FMAX_STAGES && piece_chunks <= room) stages = (int)(piece_chunks < 2 ? 2 : piece_chunks);
+    const size_t smem = (size_t)F_STAGES_AT + (size_t)stages * FSTAGE_BYTES;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(n_seqs, num_kv_heads * m_tiles, splits);
     config.blockDim = dim3(FTHREADS);
@@ -452,7 +465,7 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
     const cudaError_t status = cudaLaunchKernelEx(
         &config, decode_attention_fused_kernel, qkv, (const float2*)cos_sin, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, block_table, table_width, ctx_after, (__nv_bfloat16*)out, num_heads, num_kv_heads,
-        block_size, scale, window, splits, m_tiles, write_kv, block_shift);
+        block_size, scale, window, splits, m_tiles, write_kv, block_shift, stages);
     if (status != cudaSuccess) return fail("skv_attention_decode_fused", cudaGetErrorString(status));
     return 0;
 }

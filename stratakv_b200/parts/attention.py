@@ -29,11 +29,15 @@ def decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148
 def fused_decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148) -> int:
     """The same for the fused kernel, whose pieces are the blocks of one cluster: the largest
     power of two (other cluster sizes measured slower), at most 8, that keeps the grid within
-    two blocks per SM."""
+    two blocks per SM.  Half as many if that gives every block an SM to itself and a piece of
+    at most 512 keys, which such a block fetches whole before its inputs are ready."""
+    pairs = max(1, n_seqs * blocks_per_seq)
     by_length = max(1, max_ctx // 128)
-    by_count = 2 * sms // max(1, n_seqs * blocks_per_seq)
-    wanted = max(1, min(by_length, by_count, 8))
-    return 1 << (wanted.bit_length() - 1)
+    wanted = max(1, min(by_length, 2 * sms // pairs, 8))
+    wanted = 1 << (wanted.bit_length() - 1)
+    if wanted > 1 and pairs * wanted > sms >= pairs * wanted // 2 and max_ctx * 2 <= 512 * wanted:
+        wanted //= 2
+    return wanted
 
 
 class PagedAttention(Mixer):
