@@ -123,6 +123,12 @@ class KVCache:
     def _blocks_for(self, length: int) -> int:
         return -(-length // self.block_size)
 
+    def holds(self, slot: int, length: int) -> bool:
+        """True if the blocks that the sequence has already cover ``length`` positions in every group."""
+        record = self.sequences[slot]
+        return all(record.dropped[g.index] + len(record.blocks[g.index]) >= self._blocks_for(length)
+                   for g in self.groups)
+
     def reserve(self, wanted: Dict[int, int]) -> None:
         """``wanted``: slot -> length after the coming step.  Takes every block
         the step needs in every group, or raises ``CacheFull`` and takes none."""

@@ -56,6 +56,7 @@ class DecodeGraph:
         self.host_np = self.host.numpy()
         self.copied = torch.cuda.Event()
         self.copy_pending = False
+        self.staged = None                     # what stage_rows() last prepared, until a fill() uses it
         self.device = torch.zeros(total, dtype=torch.int32, device=engine.device)
         self._np(("token_seq"))[:] = np.arange(b)
         self._np("cu_q")[:] = np.arange(b + 1)
@@ -88,19 +89,25 @@ class DecodeGraph:
         start, count = self.offsets[name]
         return self.device[start:start + count]
 
-    def fill(self, slots: Sequence[int], tokens: Sequence[int], ctx_before: Sequence[int]) -> None:
+    def _key(self, slots: Sequence[int], ctx_before: Sequence[int]):
+        sequences = self.engine.cache.sequences
+        return tuple((slot, sequences[slot].serial, before) for slot, before in zip(slots, ctx_before))
+
+    def stage_rows(self, slots: Sequence[int], ctx_before: Sequence[int]) -> None:
+        """Everything of a step's metadata but the token ids: positions, lengths, slots, block tables.
+        It may run while the step before is still on the GPU (the engine calls it right after a launch,
+        for the step it expects next), so that only the token ids remain once they are known."""
         cache = self.engine.cache
         live = len(slots)
         b = self.bucket
         if self.copy_pending:
             self.copied.synchronize()
-        ids, pos, after, slot_ids = self._np("token_ids"), self._np("positions"), self._np("ctx_after"), self._np("slot_ids")
-        ids[:live] = tokens
+            self.copy_pending = False
+        pos, after, slot_ids = self._np("positions"), self._np("ctx_after"), self._np("slot_ids")
         pos[:live] = ctx_before
         after[:live] = pos[:live] + 1
         slot_ids[:live] = slots
         if live < b:
-            ids[live:] = 0
             pos[live:] = 0
             after[live:] = 1
             slot_ids[live:] = 0
@@ -120,6 +127,17 @@ class DecodeGraph:
                 table[row, :] = cache.trash_block
                 if row < live:
                     table[row, dropped:dropped + len(blocks)] = blocks
+        self.staged = self._key(slots, ctx_before)
+
+    def fill(self, slots: Sequence[int], tokens: Sequence[int], ctx_before: Sequence[int]) -> None:
+        if self.staged is None or self.staged != self._key(slots, ctx_before):
+            self.stage_rows(slots, ctx_before)
+        self.staged = None
+        live = len(slots)
+        ids = self._np("token_ids")
+        ids[:live] = tokens
+        if live < self.bucket:
+            ids[live:] = 0
         self.device.copy_(self.host, non_blocking=True)
         self.copied.record()
         self.copy_pending = True

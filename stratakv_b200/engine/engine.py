@@ -231,11 +231,22 @@ class Engine:
         self._io_bytes = (graph.host.numel() * 4, self._io_bytes[1])
         for slot, length in wanted.items():
             self.cache.advance(slot, length)
+        self._stage_next(graph, slots)
         if not rows:
             return None
         if len(rows) == len(entries):
             return logits[:len(entries)]
         return logits[torch.tensor(rows, device=self.device)]
+
+    def _stage_next(self, graph, slots) -> None:
+        """While the step just launched runs: prepare the metadata of the step that most likely
+        follows (the same sequences, one token further).  It takes nothing from the cache: if a
+        sequence would need a new block the work is left to the next step itself.  If another
+        step comes instead, nothing is lost: the next fill starts over."""
+        lengths = [self.cache.length(slot) for slot in slots]
+        if any(not self.cache.holds(slot, length + 1) for slot, length in zip(slots, lengths)):
+            return
+        graph.stage_rows(slots, lengths)
 
     # ---- accounting ------------------------------------------------------------------
     def kernel_launches(self) -> int:
