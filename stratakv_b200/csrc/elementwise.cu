@@ -13,13 +13,14 @@ namespace skv {
 // ---------------------------------------------------------------------------
 // x[t, :] = table[ids[t], :] widened to float.  An id outside the vocabulary
 // (hosts check before launching) writes zeros and raises the flag.
-// With `row_scale` the factor 1 / sqrt(mean(row^2) + eps_next) is left at row_scale[t] and the row
-// times `gamma_next` at scaled[t, :], for the projection after the first norm (see linear.cu).
+// With `scaled` the row times `gamma_next` is left at scaled[t, :], its sum of squares at partials[t * stride]
+// (one partial sum) and the factor 1 / sqrt(mean(row^2) + eps_next) at row_scale[t], for the projection
+// after the first norm (see linear.cu).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int hidden, int vocab, int* __restrict__ flag,
                              float* __restrict__ row_scale, const float* __restrict__ gamma_next, float eps_next,
-                             T* __restrict__ scaled) {
+                             T* __restrict__ scaled, float* __restrict__ partials, int stride) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -33,14 +34,17 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const float v = bad ? 0.0f : to_float(row[c]);
         row_out[c] = v;
-        if (row_scale) {
+        if (scaled) {
             partial = fmaf(v, v, partial);
             scaled[(size_t)t * hidden + c] = from_float<T>(v * gamma_next[c]);
         }
     }
-    if (row_scale) {
+    if (scaled) {
         const float total = block_sum(partial, scratch);
-        if (threadIdx.x == 0) row_scale[t] = 1.0f / sqrtf(total / (float)hidden + eps_next);
+        if (threadIdx.x == 0) {
+            partials[(size_t)t * stride] = total;
+            row_scale[t] = 1.0f / sqrtf(total / (float)hidden + eps_next);
+        }
     }
 }
 
@@ -236,14 +240,16 @@ SKV_EXPORT int skv_library_dtype() { return SKV_DTYPE; }
 SKV_EXPORT int skv_library_head_dim() { return SKV_HEAD_DIM; }
 
 SKV_EXPORT int skv_embed(const void* table, const int* ids, float* out, int n_tokens, int hidden,
-                         int vocab, int* flag, float* row_scale, void* scaled, const float* gamma_next,
-                         float eps_next, cudaStream_t stream) {
+                         int vocab, int* flag, void* scaled, const float* gamma_next, float* partials,
+                         int partial_stride, float* row_scale, float eps_next, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) return fail("skv_embed", "hidden and vocab must be positive");
+    if (scaled && (!gamma_next || !partials || !row_scale || partial_stride < 1))
+        return fail("skv_embed", "the next norm's weight and places for the sums of squares and the factors are needed");
     const int threads = hidden >= 1024 ? 256 : 128;
     return launch_pdl("skv_embed", embed_kernel<skv_t>, dim3(n_tokens), dim3(threads), 0, stream,
                       (const skv_t*)table, ids, out, hidden, vocab, flag, row_scale, gamma_next, eps_next,
-                      (skv_t*)scaled);
+                      (skv_t*)scaled, partials, partial_stride);
 }
 
 SKV_EXPORT int skv_rmsnorm(const float* x, const float* gamma, float eps, void* out, const int* rows,

@@ -108,13 +108,14 @@ linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void
     }
 }
 
-struct NormArgs { const float* row_scale; const int* rows; float* partials; int partial_stride; unsigned int* counter;
+struct NormArgs { const float* row_scale; const float* partials_in; int n_partials_in, stride_in; float eps_in;
+                  const int* rows; float* partials; int partial_stride; unsigned int* counter;
                   const float* gamma_next; float eps_next; void* scaled_out; float* row_scale_out; };
 
 static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                          int* flag, const NormArgs& norm, cudaStream_t stream) {
     (void)flag;
-    if (norm.row_scale || norm.partials) return fail("skv_linear(float)", "the norm-fused form exists in the bfloat16 build only");
+    if (norm.row_scale || norm.partials_in || norm.partials) return fail("skv_linear(float)", "the norm-fused form exists in the bfloat16 build only");
     dim3 grid((N + FBN - 1) / FBN, (M + FBM - 1) / FBM);
     return launch_pdl("skv_linear(float)", linear_f32_kernel, grid, dim3(256), 0, stream, (const float*)a,
                       (const float*)w, out, M, N, K, mode, act);
@@ -142,20 +143,26 @@ __device__ __forceinline__ uint4 load_weight16(const uint4* p) {
 // and multiplies its result by the factor, which is one number per token and so commutes with the
 // product.  Everything about the norm stays in float; the activations are rounded to bfloat16 once, as
 // they are when the norm runs as a kernel of its own.
-// A row's sum of squares is made in a fixed order whatever the timing: every block leaves the sum
-// over its 16 columns, and the block that finishes last (a counter tells it) adds them up in order.
+// A row's sum of squares is made in a fixed order whatever the timing: every block of the producer leaves
+// the sum over its 16 columns.  With few tokens the consumer adds them up itself: it copies the partial sums
+// of its tokens to shared memory while its main loop runs, so the producer ends without further ado.  With
+// many tokens that would be a lot of traffic for every consumer block, and the producer's block that
+// finishes last (a counter tells it) adds them up once and leaves the factor.
 struct NormArgs {
-    // consumer side (null row_scale: plain projection)
+    // consumer side: the factor itself, or the partial sums to make it from (both null: plain projection)
     const float* row_scale;        // [rows] factor of each row of X
-    const int* rows;               // token m reads row rows[m] of X and of row_scale (null: row m)
+    const float* partials_in;      // [rows, stride_in]: n_partials_in partial sums of squares per row
+    int n_partials_in, stride_in;
+    float eps_in;
+    const int* rows;               // token m reads row rows[m] of X and of the above (null: row m)
     // producer side, residual-add mode (null partials: not wanted)
-    float* partials;               // scratch [M, partial_stride], partial_stride >= blocks of the grid
+    float* partials;               // [M, partial_stride], partial_stride >= blocks of the grid
     int partial_stride;
-    unsigned int* counter;         // zero before the launch; the kernel leaves it zero
     const float* gamma_next;       // [N] weight of the norm that reads the stream next
-    float eps_next;
     __nv_bfloat16* scaled_out;     // [M, N] = bfloat16(updated out * gamma_next)
-    float* row_scale_out;          // [M] = 1 / sqrt(mean(updated out[m, :]^2) + eps_next)
+    unsigned int* counter;         // null: the consumer sums the partials; else zero before the launch and after it
+    float eps_next;
+    float* row_scale_out;          // with counter: [M] = 1 / sqrt(mean(updated out[m, :]^2) + eps_next)
 };
 
 // One block owns 16 rows of W and one chunk of 8*TG tokens.  Its warps take the
@@ -167,7 +174,7 @@ template <int TG, int U, bool STREAM, int MAX_WARPS>
 __global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS == 4 ? (TG == 1 ? 5 : (TG == 2 ? 4 : 2)) : (MAX_WARPS == 8 && TG <= 2 ? 2 : 1))
 skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                           void* __restrict__ out, int M, int N, int K, int mode, int act, const NormArgs norm) {
-    extern __shared__ float red[];                 // [warps][16][8*TG + 1]
+    extern __shared__ float red[];                 // [warps][16][8*TG + 1], [8*TG] factors, [8*TG][n_partials_in] partial sums
     constexpr int COLS = 8 * TG, PITCH = COLS + 1;
     pdl_launch_dependents();
     const int warps = blockDim.x >> 5;
@@ -204,7 +211,19 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
         const int safe = min(m, M - 1);
         x_ptr[t] = X + (size_t)(norm.rows ? norm.rows[safe] : safe) * K + tig * 8;
     }
-    if (norm.row_scale && !norm.rows && threadIdx.x * 32 < M) {
+    float* factor = red + (size_t)warps * 16 * PITCH;
+    float* staged = factor + COLS;
+    if (norm.partials_in) {
+        // the partial sums are wanted after the main loop: they travel to shared memory meanwhile
+        for (int i = threadIdx.x; i < COLS * norm.n_partials_in; i += blockDim.x) {
+            const int m = i / norm.n_partials_in, p = i - m * norm.n_partials_in;
+            if (m0 + m < M) {
+                const float* src = norm.partials_in + (size_t)(norm.rows ? norm.rows[m0 + m] : m0 + m) * norm.stride_in + p;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(staged + i)), "l"(src) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    } else if (norm.row_scale && !norm.rows && threadIdx.x * 32 < M) {
         // the factors are wanted after the main loop: bring their lines close meanwhile
         asm volatile("prefetch.global.L1 [%0];" ::"l"(norm.row_scale + threadIdx.x * 32));
     }
@@ -226,6 +245,16 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
             }
         }
     }
+    if (norm.partials_in) {
+        asm volatile("cp.async.wait_all;\n" ::: "memory");
+        __syncthreads();
+        for (int m = warp; m < COLS; m += warps) {          // one token per warp at a time, lanes in a fixed order
+            float total = 0.0f;
+            for (int p = lane; p < norm.n_partials_in; p += 32) total += staged[m * norm.n_partials_in + p];
+            total = warp_sum(total);
+            if (lane == 0) factor[m] = 1.0f / sqrtf(total / (float)K + norm.eps_in);
+        }
+    }
     float* mine = red + (size_t)warp * 16 * PITCH;
 #pragma unroll
     for (int t = 0; t < TG; ++t) {
@@ -239,7 +268,8 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
         const int r = idx & 15, m = idx >> 4;
         float sum = 0.0f;
         for (int w = 0; w < warps; ++w) sum += red[((size_t)w * 16 + r) * PITCH + m];
-        if (norm.row_scale && m0 + m < M) sum *= norm.row_scale[norm.rows ? norm.rows[m0 + m] : m0 + m];
+        if (norm.partials_in) sum *= factor[m];
+        else if (norm.row_scale && m0 + m < M) sum *= norm.row_scale[norm.rows ? norm.rows[m0 + m] : m0 + m];
         red[(size_t)r * PITCH + m] = sum;          // warp 0's tile becomes the total
         // (each (r, m) is read and written by this thread only)
     }
@@ -270,7 +300,8 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
             for (int offset = 8; offset > 0; offset >>= 1) square += __shfl_xor_sync(0xffffffffu, square, offset);
             if (r == 0 && m0 + m < M) norm.partials[(size_t)(m0 + m) * norm.partial_stride + blockIdx.x] = square;
         }
-        // the last block to get here adds the partial sums up (the grid has one chunk of tokens: M <= 8*TG)
+        if (!norm.counter) return;                  // the consumer adds the partial sums up
+        // the last block to get here adds them up (the grid has one chunk of tokens: M <= 8*TG)
         __shared__ bool last;
         __threadfence();
         __syncthreads();
@@ -299,7 +330,8 @@ template <int TG, int U, int MAX_WARPS>
 static int launch_skinny_as(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                             int warps, const NormArgs& norm, cudaStream_t stream) {
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
-    const size_t smem = (size_t)warps * 16 * (8 * TG + 1) * sizeof(float);
+    const size_t smem = ((size_t)warps * 16 * (8 * TG + 1) + 8 * TG + (size_t)8 * TG * (norm.partials_in ? norm.n_partials_in : 0)) * sizeof(float);
+    if (smem > 48 * 1024) return fail("skv_linear(bfloat16)", "too many partial sums for the consumer to stage: let the producer finish them");
     dim3 grid(row_tiles, chunks);
     if (chunks == 1)
         return launch_pdl("skv_linear(bfloat16)", skinny_linear_bf16_kernel<TG, U, true, MAX_WARPS>, grid,
@@ -347,7 +379,7 @@ static int launch_linear(const void* a, const void* w, void* out, int M, int N, 
         return fail("skv_linear(bfloat16)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15)
         return fail("skv_linear(bfloat16)", "operands must be 16-byte aligned");
-    if ((norm.row_scale || norm.partials) && M > 64)
+    if ((norm.row_scale || norm.partials_in || norm.partials) && M > 64)
         return fail("skv_linear(bfloat16)", "the norm-fused form serves steps of at most 64 tokens");
     if (M > 64 && tcgen05_enabled()) return linear_tcgen05(a, w, out, M, N, K, mode, flag, stream);
     // at most 8 warps and under 100 registers a thread: two blocks fit on an SM, so the next
@@ -374,39 +406,50 @@ static int check_linear(int M, int N, int K, int mode, int act) {
 }
 
 // `flag` (may be null): bit 2 (value 4) is raised if a pipeline wait inside a kernel timed out.
-// With `row_scale_out` (residual-add mode, at most 64 tokens, bfloat16 build) the kernel also leaves what the
-// projection after the next norm needs (see NormArgs); `partials` is scratch of [M, partial_stride] floats with
-// partial_stride >= N/16 rounded up, `counter` one zeroed word that the kernel leaves zeroed.
+// With `scaled_out` (residual-add mode, at most 64 tokens, bfloat16 build) the kernel also leaves what the
+// projection after the next norm needs (see NormArgs): the scaled rows, and the rows' sums of squares as
+// `partials` [M, partial_stride] with partial_stride >= N/16 rounded up.  With `counter` (one zeroed word, left
+// zeroed) it finishes them into `row_scale_out` too.
 SKV_EXPORT int skv_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
-                          int* flag, float* row_scale_out, void* scaled_out, const float* gamma_next, float eps_next,
-                          float* partials, int partial_stride, unsigned int* counter, cudaStream_t stream) {
+                          int* flag, void* scaled_out, const float* gamma_next, float* partials, int partial_stride,
+                          float* row_scale_out, float eps_next, unsigned int* counter, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (int code = check_linear(M, N, K, mode, act)) return code;
     NormArgs norm = {};
-    if (row_scale_out) {
+    if (scaled_out) {
         if (mode != MODE_ADD_F32) return fail("skv_linear", "a norm is folded into the residual-add mode only");
-        if (!gamma_next || !scaled_out || !partials || !counter || partial_stride < (N + 15) / 16)
-            return fail("skv_linear", "the next norm's weight, a place for the scaled rows, scratch for N/16 partial sums per token and a counter are needed");
+        if (!gamma_next || !partials || partial_stride < (N + 15) / 16 || (counter && !row_scale_out))
+            return fail("skv_linear", "the next norm's weight, room for N/16 partial sums per token and, with a counter, a place for the factors are needed");
         norm.partials = partials;
         norm.partial_stride = partial_stride;
-        norm.counter = counter;
         norm.gamma_next = gamma_next;
-        norm.eps_next = eps_next;
         norm.scaled_out = (decltype(norm.scaled_out))scaled_out;
+        norm.counter = counter;
+        norm.eps_next = eps_next;
         norm.row_scale_out = row_scale_out;
     }
     return launch_linear(a, w, out, M, N, K, mode, act, flag, norm, stream);
 }
 
 // The projection after a folded norm: `a` holds rows of (stream * norm weight) in bfloat16, token m reads
-// row rows[m] (or m), and the result is multiplied by row_scale[that row].  bfloat16 build, at most 64 tokens.
-SKV_EXPORT int skv_linear_normed(const void* a, const float* row_scale, const int* rows, const void* w, void* out,
-                                 int M, int N, int K, int mode, int act, cudaStream_t stream) {
+// row rows[m] (or m), and the result is multiplied by the row's factor: row_scale[row], or (row_scale null)
+// 1 / sqrt(sum of partials[row, :n_partials] / K + eps).  bfloat16 build, at most 64 tokens.
+SKV_EXPORT int skv_linear_normed(const void* a, const float* row_scale, const float* partials, int n_partials,
+                                 int partial_stride, float eps, const int* rows, const void* w, void* out, int M,
+                                 int N, int K, int mode, int act, cudaStream_t stream) {
     if (M <= 0) return 0;
     if (int code = check_linear(M, N, K, mode, act)) return code;
-    if (!row_scale) return fail("skv_linear_normed", "the rows' factors are needed");
+    if (!row_scale && (!partials || n_partials <= 0 || partial_stride < n_partials))
+        return fail("skv_linear_normed", "the rows' factors, or their partial sums of squares, are needed");
     NormArgs norm = {};
-    norm.row_scale = row_scale;
+    if (row_scale) {
+        norm.row_scale = row_scale;
+    } else {
+        norm.partials_in = partials;
+        norm.n_partials_in = n_partials;
+        norm.stride_in = partial_stride;
+        norm.eps_in = eps;
+    }
     norm.rows = rows;
     return launch_linear(a, w, out, M, N, K, mode, act, nullptr, norm, stream);
 }

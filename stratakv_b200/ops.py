@@ -28,7 +28,7 @@ def _ptr(tensor: Optional[torch.Tensor]):
 
 
 _NULL = ctypes.c_void_p(0)
-_NO_FOLD = (_NULL, _NULL, _NULL, ctypes.c_float(0.0), _NULL, 0, _NULL)
+_NO_FOLD = (_NULL, _NULL, _NULL, 0, _NULL, ctypes.c_float(0.0), _NULL)
 _SCOPED_STREAM = None
 
 
@@ -104,13 +104,13 @@ class Kernels:
             raise KernelError("embed: shapes do not agree")
         fold = self._fold_target(stats, n, hidden)
         self._check(self.lib.skv_embed(_ptr(table), _ptr(ids), _ptr(out), n, hidden, vocab, _ptr(flag),
-                                       *(fold[:4] if fold else _NO_FOLD[:4]), _stream()), "embed")
+                                       *(fold[:6] if fold else _NO_FOLD[:6]), _stream()), "embed")
         if stats is not None:
-            stats.filled() if fold else stats.invalidate()
+            stats.filled(1 if stats.consumer_sums else 0) if fold else stats.invalidate()
 
     def _fold_target(self, stats, rows: int, width: int):
-        """Arguments (rows' factors, scaled rows, next norm's weight and eps, scratch for partial sums, its
-        stride, counter) for a kernel that writes ``rows`` rows of the stream; None where it cannot fold."""
+        """Arguments (scaled rows, next norm's weight, partial sums, their stride, rows' factors, next norm's
+        eps, counter) for a kernel that writes ``rows`` rows of the stream; None where it cannot fold."""
         if stats is None or stats.next_norm is None or self.dtype != torch.bfloat16 or rows > MAX_FUSED_ROWS:
             return None
         gamma = stats.next_norm.gamma
@@ -121,8 +121,8 @@ class Kernels:
                 or stats.partials.shape[0] != rows
                 or stats.partials.shape[1] * COLUMNS_PER_PARTIAL < width):
             raise KernelError("the buffers of the folded norm do not match the stream")
-        return (_ptr(stats.row_scale), _ptr(stats.scaled), _ptr(gamma), ctypes.c_float(stats.next_norm.spec.eps),
-                _ptr(stats.partials), stats.partials.shape[1], _ptr(stats.counter))
+        return (_ptr(stats.scaled), _ptr(gamma), _ptr(stats.partials), stats.partials.shape[1], _ptr(stats.row_scale),
+                ctypes.c_float(stats.next_norm.spec.eps), _NULL if stats.consumer_sums else _ptr(stats.counter))
 
     def rmsnorm(self, x, gamma, eps: float, out, rows=None):
         """out[r, :] = rmsnorm(x[rows[r] or r, :]) * gamma, in the compute dtype."""
@@ -173,8 +173,16 @@ class Kernels:
         if normed is not None:
             if stats is not None:
                 raise KernelError("linear: a folded norm on the input and statistics of the output do not go together")
+            if normed.n_partials > 0:
+                self._want(normed.partials, torch.float32, "partials")
+                if normed.partials.shape[0] != normed.scaled.shape[0] or normed.partials.shape[1] < normed.n_partials:
+                    raise KernelError("linear: the partial sums do not match the normalised input")
+                factor = (_NULL, _ptr(normed.partials), normed.n_partials, normed.partials.shape[1],
+                          ctypes.c_float(normed.eps))
+            else:
+                factor = (_ptr(normed.row_scale), _NULL, 0, 0, ctypes.c_float(0.0))
             self._check(self.lib.skv_linear_normed(
-                _ptr(normed.scaled), _ptr(normed.row_scale), _ptr(normed.rows), _ptr(w), _ptr(out), M, N, K, mode,
+                _ptr(normed.scaled), *factor, _ptr(normed.rows), _ptr(w), _ptr(out), M, N, K, mode,
                 ACTIVATIONS[activation], _stream()), "linear")
             return
         fold = self._fold_target(stats, M, N)
@@ -183,7 +191,7 @@ class Kernels:
                     "linear")
         if stats is not None:
             if fold:
-                stats.filled()
+                stats.filled((N + COLUMNS_PER_PARTIAL - 1) // COLUMNS_PER_PARTIAL if stats.consumer_sums else 0)
             else:
                 stats.invalidate()
 

@@ -26,7 +26,7 @@ class RMSNorm(Norm):
     def forward(self, x, rows=None, out=None, name="normed", stats=None):
         """``stats`` prepared for this norm: leave the rest of the work to the consumer's projection."""
         if stats is not None and out is None and stats.ready_for(self):
-            return NormedRows(stats.scaled, stats.row_scale, rows)
+            return NormedRows(stats.scaled, stats.row_scale, rows, stats.partials, stats.n_partials, self.spec.eps)
         n_rows = x.shape[0] if rows is None else rows.numel()
         if out is None:
             out = self.rt.workspace.get(name, (n_rows, self.spec.size), self.rt.dtype)

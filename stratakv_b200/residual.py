@@ -6,9 +6,12 @@ costs a launch and a round trip through memory for almost no work.  RMSNorm is
 factor per row commutes with the projection that follows.  So the kernel that
 writes the stream (the embedding, a residual-add projection) also leaves, in a
 ``ResidualStats``, each row times the weight of the norm that reads the stream
-next (in the compute dtype) and the row's factor; that norm then hands over
-``NormedRows`` instead of running, and its consumer's first projection
-multiplies its result by the factor.  All of the norm's arithmetic stays in
+next (in the compute dtype) and what gives the row's factor; that norm then
+hands over ``NormedRows`` instead of running, and its consumer's first
+projection multiplies its result by the factor.  With few rows the writer only
+leaves partial sums of squares (one per block of the kernel) and the consumer
+adds them up while it loads its weights; with more, that would be much traffic
+for every block of the consumer, and the writer's last block makes the factor.  All of the norm's arithmetic stays in
 float32 and the activations are rounded once, as with the separate kernel; only
 the place of that rounding (before the factor instead of after it) differs.
 
@@ -26,18 +29,21 @@ from typing import Any, Optional
 import torch
 
 MAX_FUSED_ROWS = 64        # the small-batch projection kernel serves at most this many tokens
+CONSUMER_SUMS_ROWS = 16    # up to here the consumer adds the partial sums up, beyond the writer does
 COLUMNS_PER_PARTIAL = 16   # a residual-add projection sums squares over 16 columns per block
 
 
 class ResidualStats:
-    """``scaled[row]`` is the stream's row times ``prepared_for.gamma`` and ``row_scale[row]``
-    that norm's factor for the row, while ``prepared_for`` is not None."""
+    """While ``prepared_for`` is not None: ``scaled[row]`` is the stream's row times
+    ``prepared_for.gamma``, and that norm's factor for the row is ``row_scale[row]`` if
+    ``n_partials`` is 0, else ``1 / sqrt(sum(partials[row, :n_partials]) / width + eps)``."""
 
     def __init__(self, scaled: torch.Tensor, row_scale: torch.Tensor, partials: torch.Tensor, counter: torch.Tensor):
         self.scaled = scaled
         self.row_scale = row_scale
-        self.partials = partials       # scratch of the writing kernel: [rows, >= width / 16]
+        self.partials = partials       # [rows, >= width / 16]
         self.counter = counter         # one int32, zero between kernels
+        self.n_partials = 0
         self.next_norm: Any = None
         self.prepared_for: Any = None
 
@@ -52,8 +58,14 @@ class ResidualStats:
     def expect(self, norm) -> None:
         self.next_norm = norm
 
-    def filled(self) -> None:
+    @property
+    def consumer_sums(self) -> bool:
+        # (the consumer stages rows x partial sums in shared memory: keep that within 32 KB)
+        return self.scaled.shape[0] <= CONSUMER_SUMS_ROWS and self.partials.shape[1] <= 512
+
+    def filled(self, n_partials: int = 0) -> None:
         self.prepared_for = self.next_norm
+        self.n_partials = n_partials
 
     def invalidate(self) -> None:
         self.prepared_for = None
@@ -64,11 +76,15 @@ class ResidualStats:
 
 @dataclass
 class NormedRows:
-    """A norm not yet finished: ``scaled[rows]`` still lacks the factor per row, ``row_scale[rows]``,
-    which the consuming projection applies to its result."""
+    """A norm not yet finished: ``scaled[rows]`` still lacks the factor per row, which the consuming
+    projection applies to its result: ``row_scale[rows]``, or (``n_partials`` > 0) made from the
+    rows' partial sums of squares and ``eps``."""
     scaled: torch.Tensor
     row_scale: torch.Tensor
     rows: Optional[torch.Tensor] = None
+    partials: Optional[torch.Tensor] = None
+    n_partials: int = 0
+    eps: float = 0.0
 
     @property
     def shape(self):

@@ -124,7 +124,7 @@ def _stats(rows, width, dtype=torch.bfloat16, spare=0):
 def _folded(stats, norm, rows=None):
     from stratakv_b200.residual import NormedRows
     assert stats.ready_for(norm)
-    return NormedRows(stats.scaled, stats.row_scale, rows)
+    return NormedRows(stats.scaled, stats.row_scale, rows, stats.partials, stats.n_partials, norm.spec.eps)
 
 
 @pytest.mark.parametrize("M,N,K,hidden_out", [(1, 176, 64, 72), (5, 104, 80, 40), (8, 2560, 2048, 2048),
@@ -146,8 +146,14 @@ def test_linear_with_folded_norm(M, N, K, hidden_out):
 
     def check(norm):
         eps = norm.spec.eps
-        factor = torch.rsqrt((x.double() ** 2).mean(-1) + eps)
-        assert torch.allclose(stats.row_scale.double(), factor, rtol=1e-5, atol=0)
+        if stats.consumer_sums:        # few rows: partial sums of squares for the consumer to add up
+            assert stats.n_partials > 0
+            sums = stats.partials[:, :stats.n_partials].double().sum(-1)
+            assert torch.allclose(sums, (x.double() ** 2).sum(-1), rtol=1e-5, atol=0)
+        else:                          # more: the writer's last block has made the factor
+            assert stats.n_partials == 0
+            factor = torch.rsqrt((x.double() ** 2).mean(-1) + eps)
+            assert torch.allclose(stats.row_scale.double(), factor, rtol=1e-5, atol=0)
         assert torch.equal(stats.scaled, (x * norm.gamma).to(dtype))
         assert int(stats.counter) == 0
         for selected in (None, rows):
@@ -221,6 +227,9 @@ def test_folded_norm_refusals():
     with pytest.raises(KernelError, match="at most 64 tokens"):
         k.linear(NormedRows(stats.scaled, stats.row_scale), w, torch.zeros(80, 32, device="cuda"),
                  ops.MODE_STORE_F32)
+    with pytest.raises(KernelError, match="partial sums do not match"):
+        k.linear(NormedRows(stats.scaled[:8], stats.row_scale[:8], None, stats.partials[:8], 9, 1e-5), w,
+                 torch.zeros(8, 32, device="cuda"), ops.MODE_STORE_F32)
     # more rows than the kernel folds a norm for: the sum is made, nothing is left for the norm
     norm = _Norm(torch.ones(64, device="cuda"), 1e-5)
     stats.expect(norm)
