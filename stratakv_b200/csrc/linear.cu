@@ -214,12 +214,21 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
     float* factor = red + (size_t)warps * 16 * PITCH;
     float* staged = factor + COLS;
     if (norm.partials_in) {
-        // the partial sums are wanted after the main loop: they travel to shared memory meanwhile
-        for (int i = threadIdx.x; i < COLS * norm.n_partials_in; i += blockDim.x) {
-            const int m = i / norm.n_partials_in, p = i - m * norm.n_partials_in;
+        // the partial sums are wanted after the main loop: they travel to shared memory meanwhile, 16 bytes
+        // at a time where the rows allow it (the row in shared memory is `pitch` floats)
+        const bool wide = (norm.stride_in & 3) == 0 && ((uintptr_t)norm.partials_in & 15) == 0;
+        const int pitch = (norm.n_partials_in + 3) & ~3;
+        const int pieces = wide ? pitch >> 2 : norm.n_partials_in;
+        for (int i = threadIdx.x; i < COLS * pieces; i += blockDim.x) {
+            const int m = i / pieces, piece = i - m * pieces;
             if (m0 + m < M) {
-                const float* src = norm.partials_in + (size_t)(norm.rows ? norm.rows[m0 + m] : m0 + m) * norm.stride_in + p;
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(staged + i)), "l"(src) : "memory");
+                const float* row = norm.partials_in + (size_t)(norm.rows ? norm.rows[m0 + m] : m0 + m) * norm.stride_in;
+                if (wide)
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(staged + m * pitch + 4 * piece)),
+                                 "l"(row + 4 * piece) : "memory");
+                else
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(staged + m * pitch + piece)),
+                                 "l"(row + piece) : "memory");
             }
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -250,7 +259,8 @@ skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat
         __syncthreads();
         for (int m = warp; m < COLS; m += warps) {          // one token per warp at a time, lanes in a fixed order
             float total = 0.0f;
-            for (int p = lane; p < norm.n_partials_in; p += 32) total += staged[m * norm.n_partials_in + p];
+            const int pitch = (norm.n_partials_in + 3) & ~3;
+            for (int p = lane; p < norm.n_partials_in; p += 32) total += staged[m * pitch + p];
             total = warp_sum(total);
             if (lane == 0) factor[m] = 1.0f / sqrtf(total / (float)K + norm.eps_in);
         }
@@ -330,7 +340,7 @@ template <int TG, int U, int MAX_WARPS>
 static int launch_skinny_as(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                             int warps, const NormArgs& norm, cudaStream_t stream) {
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
-    const size_t smem = ((size_t)warps * 16 * (8 * TG + 1) + 8 * TG + (size_t)8 * TG * (norm.partials_in ? norm.n_partials_in : 0)) * sizeof(float);
+    const size_t smem = ((size_t)warps * 16 * (8 * TG + 1) + 8 * TG + (size_t)8 * TG * (norm.partials_in ? (norm.n_partials_in + 3) & ~3 : 0)) * sizeof(float);
     if (smem > 48 * 1024) return fail("skv_linear(bfloat16)", "too many partial sums for the consumer to stage: let the producer finish them");
     dim3 grid(row_tiles, chunks);
     if (chunks == 1)

@@ -51,6 +51,7 @@ class ResidualStats:
     def allocate(cls, get, rows: int, width: int, dtype):
         """Buffers from ``get(name, shape, dtype, zero=False)`` (a workspace's)."""
         partial_width = (width + COLUMNS_PER_PARTIAL - 1) // COLUMNS_PER_PARTIAL
+        partial_width = (partial_width + 3) // 4 * 4      # rows of whole 16 bytes: the consumer copies them so
         return cls(get("residual_scaled", (rows, width), dtype), get("residual_row_scale", (rows,), torch.float32),
                    get("residual_partials", (rows, partial_width), torch.float32),
                    get("residual_counter", (1,), torch.int32, zero=True))
