@@ -97,9 +97,16 @@ def toy_plain(tensors, tokens):
     return plain_llama.rmsnorm(x, w["norm"], 1e-5) @ w["emb"].T
 
 
-def test_toy_mixer_with_state_is_registered_built_and_stepped():
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
+    """In bfloat16 the decode steps fold the norms of the built-in parts into their projections; the toy
+    mixer knows nothing of that, so the norm before it runs as a kernel and the one after it too."""
     from stratakv_b200 import StepEntry
-    engine, tensors = toy_model("float32")
+    from helpers import tolerance
+    engine, tensors = toy_model(dtype)
+    rtol, atol = tolerance(dtype)
+    if dtype == "bfloat16":
+        tensors = {k: (v if v.dim() == 1 or k == "l1.mix" else v.to(torch.bfloat16).float()) for k, v in tensors.items()}
     assert engine.cache.state(1).shape == (engine.cache.max_slots, 4 * 49)
     assert len(engine.cache.groups) == 1 and engine.cache.entry_group[1] == (-1, -1)
     a, b = random_tokens(120, 30, seed=1), random_tokens(120, 11, seed=2)
@@ -107,13 +114,13 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     for round_ in range(2):                                  # the second round reuses slots: state must be zeroed
         sa, sb = engine.open_sequence(), engine.open_sequence()
         got = engine.step([StepEntry(sa, a[:20], [19]), StepEntry(sb, b[:4], [0, 3])]).cpu().numpy()
-        np.testing.assert_allclose(got, np.stack([ref_a[19], ref_b[0], ref_b[3]]), rtol=1e-4, atol=2e-5)
+        np.testing.assert_allclose(got, np.stack([ref_a[19], ref_b[0], ref_b[3]]), rtol=rtol, atol=atol)
         for position in range(4, 11):
             got = engine.step([StepEntry(sa, [a[16 + position]], [0]), StepEntry(sb, [b[position]], [0])]).cpu().numpy()
-            np.testing.assert_allclose(got, np.stack([ref_a[16 + position], ref_b[position]]), rtol=1e-4, atol=2e-5)
+            np.testing.assert_allclose(got, np.stack([ref_a[16 + position], ref_b[position]]), rtol=rtol, atol=atol)
         engine.close_sequence(sb)
         got = engine.step([StepEntry(sa, a[27:], [2])]).cpu().numpy()
-        np.testing.assert_allclose(got[0], ref_a[29], rtol=1e-4, atol=2e-5)
+        np.testing.assert_allclose(got[0], ref_a[29], rtol=rtol, atol=atol)
         engine.close_sequence(sa)
         assert engine.cache.all_free()
 
