@@ -160,3 +160,36 @@ def test_batches_that_do_not_fill_a_graph_bucket(folders, plain, dtype):
         for r in requests:
             engine.close_sequence(r["slot"])
         assert engine.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_slot_taken_again_at_the_same_length(folders, plain, dtype):
+    """Decode steps prepare the next step's positions and block tables ahead.  A request that ends and
+    another that takes its slot and happens to stand at the same length must not inherit them: the
+    second request's blocks are others (the first request's blocks are held by a third one meanwhile)."""
+    from stratakv_b200 import StepEntry
+    name = "B"
+    vocab = TINY[name]["vocab_size"]
+    engine = engine_for(folders[name], dtype, max_tokens=1024, block_size=16)
+    first, second, third = (random_tokens(vocab, 40, seed=s) for s in (71, 72, 73))
+    slot = engine.open_sequence()
+    engine.step([StepEntry(slot, first[:30], [])])
+    for position in range(30, 36):
+        got = engine.step([StepEntry(slot, [first[position]], [0])])
+        check(got[0], plain(name, first)[position], dtype, f"first request, position {position}")
+    engine.close_sequence(slot)
+    keeper = engine.open_sequence()                      # takes the slot and the blocks just given back
+    engine.step([StepEntry(keeper, third[:36], [])])
+    again = engine.open_sequence()
+    engine.step([StepEntry(again, second[:30], [])])
+    engine.close_sequence(keeper)
+    slot = engine.open_sequence()
+    assert slot == keeper
+    engine.step([StepEntry(slot, third[:30], [])])
+    for position in range(30, 36):
+        got = engine.step([StepEntry(again, [second[position]], [0]), StepEntry(slot, [third[position]], [0])])
+        check(got[0], plain(name, second)[position], dtype, f"second request, position {position}")
+        check(got[1], plain(name, third)[position], dtype, f"third request, position {position}")
+    engine.close_sequence(slot)
+    engine.close_sequence(again)
+    assert engine.cache.all_free()
