@@ -403,6 +403,181 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// ---- few tokens: the weights take the 128 rows of the instruction ---------------------------------
+// For steps of 17 to 128 tokens the tile above would use a fraction of its 128 token rows and leave most SMs
+// without a tile.  Here the operands change places: D^T[128 weight rows, tokens] = W_tile . X^T, so a block
+// owns 128 rows of W (all of K, or one of `splits` parts of it) and every token; the grid has N/128 x splits
+// blocks that stream their weights once, through a deep ring, with the first stages requested before the
+// wait on the kernel in front (weights do not depend on it).  In the epilogue a thread holds one weight
+// row's results for 32 tokens at a time, and the 32 lanes of a warp write 32 neighbouring columns of a
+// token's output row.  With splits > 1 the blocks of a cluster each take a part of K; the others push their
+// accumulators into the first block's shared memory, which adds them in rank order.
+template <int MP, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                               void* __restrict__ out, int M, int N, int K, int mode, int splits,
+                               int* __restrict__ flag) {
+    constexpr uint32_t W_BYTES = 128 * TC_BK * 2, X_BYTES = MP * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(tiles + (size_t)STAGES * STAGE_BYTES);      // full[STAGES], empty[STAGES], acc_full
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 128;
+    const int split = blockIdx.y;                                           // == rank in the cluster
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    const int per_split = (k_blocks + splits - 1) / splits;
+    const int k_first = split * per_split, k_iters = max(0, min(k_blocks, k_first + per_split) - k_first);
+    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES), acc_full = smem_addr(bars + 2 * STAGES);
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)MP) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- loader: weights of the first stages before the wait, activations after it ----------------
+        bool ok = true;
+        const int ahead = min(STAGES, k_iters);
+        for (int i = 0; i < ahead; ++i) {
+            mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+            tma_load_2d(smem_addr(tiles + (size_t)i * STAGE_BYTES), &map_w, (k_first + i) * TC_BK, n0, full0 + 8 * i);
+        }
+        pdl_wait();
+        for (int i = 0; i < ahead; ++i)
+            tma_load_2d(smem_addr(tiles + (size_t)i * STAGE_BYTES) + W_BYTES, &map_x, (k_first + i) * TC_BK, 0, full0 + 8 * i);
+        for (int i = ahead; i < k_iters && ok; ++i) {
+            const int s = i % STAGES;
+            ok = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, flag);
+            if (!ok) break;
+            const uint32_t dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+            mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+            tma_load_2d(dst, &map_w, (k_first + i) * TC_BK, n0, full0 + 8 * s);
+            tma_load_2d(dst + W_BYTES, &map_x, (k_first + i) * TC_BK, 0, full0 + 8 * s);
+        }
+        if (!ok) {
+            for (int i = max(0, k_iters - STAGES); i < k_iters; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- tensor-core issue ------------------------------------------------------------------------
+        constexpr uint32_t idesc = umma_idesc(128, MP);
+        bool ok = true;
+        for (int i = 0; i < k_iters && ok; ++i) {
+            const int s = i % STAGES;
+            ok = mbar_wait(full0 + 8 * s, (i / STAGES) & 1, flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t w_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+            const uint64_t w_desc = umma_desc(w_addr), x_desc = umma_desc(w_addr + W_BYTES);
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k)
+                umma_bf16(tmem_base, w_desc + 2 * k, x_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit(empty0 + 8 * s);
+        }
+        if (ok) umma_commit(acc_full);            // arrives when every MMA has finished (at once if there were none)
+    }
+    // ---- epilogue: warps 2-5, one weight row per thread -----------------------------------------------
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;          // weight row within the tile = TMEM lane
+    const int n = n0 + row;
+    bool ok = true;
+    if (warp >= 2) {
+        pdl_wait();                               // the residual stream that the epilogue reads is the kernels' before
+        ok = k_iters == 0 || mbar_wait(acc_full, 0, flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    auto read_accumulator = [&](int c, uint32_t (&v)[32]) {
+        if (ok && k_iters > 0) {
+            tmem_load_32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+    };
+    // With splits, the partial results [tokens][128 rows] of ranks 1.. go to rank 0's shared memory, where the
+    // pipeline's stages lay: the first cluster barrier is passed when every block's main loop is over (the
+    // epilogue warps get there after their accumulator is complete), the second when the pushes are done.
+    float* inbox = (float*)tiles;                 // [splits - 1][MP][128] floats, in rank 0
+    if (splits > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (split > 0 && warp >= 2) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(inbox)), "r"(0));
+            remote += (uint32_t)(split - 1) * MP * 128 * 4;
+#pragma unroll 1
+            for (int c = 0; c < MP && c < M; c += 32) {
+                uint32_t v[32];
+                read_accumulator(c, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + (uint32_t)((c + j) * 128 + row) * 4), "r"(v[j]) : "memory");
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    if (warp >= 2 && split == 0) {
+#pragma unroll 1
+        for (int c = 0; c < MP && c < M; c += 32) {
+            uint32_t v[32];
+            read_accumulator(c, v);
+            for (int r = 1; r < splits; ++r) {    // rank order: the sum does not depend on timing
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    v[j] = __float_as_uint(__uint_as_float(v[j]) + inbox[((size_t)(r - 1) * MP + c + j) * 128 + row]);
+            }
+            if (mode == TC_MODE_GATED) {
+                // rows come in groups of 16: 8 gate rows, then their 8 up rows; lane l < 8 (mod 16) pairs with l + 8
+                const int half_n = N >> 1;
+                const int o = ((n >> 4) << 3) + (n & 7);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float up = __shfl_down_sync(0xffffffffu, __uint_as_float(v[j]), 8);
+                    if ((lane & 8) == 0 && c + j < M && n < N)
+                        ((__nv_bfloat16*)out)[(size_t)(c + j) * half_n + o] =
+                            __float2bfloat16_rn(silu_gate(__uint_as_float(v[j])) * up);
+                }
+            } else if (n < N) {
+                if (mode == TC_MODE_STORE) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c + j < M) ((__nv_bfloat16*)out)[(size_t)(c + j) * N + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                } else if (mode == TC_MODE_STORE_F32) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c + j < M) ((float*)out)[(size_t)(c + j) * N + n] = __uint_as_float(v[j]);
+                } else {
+                    float old[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) old[j] = c + j < M ? __ldcg((const float*)out + (size_t)(c + j) * N + n) : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c + j < M) ((float*)out)[(size_t)(c + j) * N + n] = old[j] + __uint_as_float(v[j]);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)MP) : "memory");
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -505,11 +680,60 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
                       map_a, map_w, map_out, tma_out, out, M, N, K, mode, flag);
 }
 
+template <int MP, int STAGES>
+static int launch_few_tokens(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
+                             cudaStream_t stream) {
+    CUtensorMap map_w, map_x;
+    if (int code = tensor_map(w, N, K, 2, 128, TC_BK, &map_w)) return code;
+    if (int code = tensor_map(a, M, K, 2, MP, TC_BK, &map_x)) return code;
+    constexpr size_t ring = (size_t)STAGES * (128 * TC_BK * 2 + MP * TC_BK * 2);
+    constexpr size_t smem = ring + (2 * STAGES + 1) * 8 + 16 + 1024;
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0, count = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+            return fail("skv_linear(tcgen05)", "cannot read the number of SMs");
+        cudaError_t status = cudaFuncSetAttribute(gemm_tcgen05_few_tokens_kernel<MP, STAGES>,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("skv_linear(tcgen05)", cudaGetErrorString(status));
+        sm_count = count;
+    }
+    // Parts of K per tile of 128 weight rows: the largest power of two that keeps the grid within the GPU, leaves
+    // every part at least four 64-wide steps, and whose partial results fit where the pipeline's stages were.
+    const int n_tiles = (N + 127) / 128, k_blocks = (K + TC_BK - 1) / TC_BK;
+    int splits = 1;
+    while (splits < 8 && n_tiles * splits * 2 <= sm_count && k_blocks >= splits * 2 * 4 &&
+           (size_t)(splits * 2 - 1) * MP * 128 * 4 <= ring)
+        splits *= 2;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)n_tiles, (unsigned)splits, 1);
+    config.blockDim = dim3(TC_THREADS);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 1;
+    attributes[0].val.clusterDim.y = (unsigned)splits;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = pdl_enabled() ? 2 : 1;
+    const cudaError_t status = cudaLaunchKernelEx(&config, gemm_tcgen05_few_tokens_kernel<MP, STAGES>, map_w, map_x, out,
+                                                  M, N, K, mode, splits, flag);
+    if (status != cudaSuccess) return fail("skv_linear(tcgen05)", cudaGetErrorString(status));
+    return 0;
+}
+
 int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
                    cudaStream_t stream) {
     if (K % 8 != 0) return fail("skv_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_linear(tcgen05)", "operands must be 16-byte aligned");
     if (mode == TC_MODE_GATED && N % 16 != 0) return fail("skv_linear(tcgen05)", "a gated weight needs a multiple of 16 rows");
+    if (M <= 32) return launch_few_tokens<32, 8>(a, w, out, M, N, K, mode, flag, stream);
+    if (M <= 64) return launch_few_tokens<64, 8>(a, w, out, M, N, K, mode, flag, stream);
+    if (M <= 128) return launch_few_tokens<128, 6>(a, w, out, M, N, K, mode, flag, stream);
     // Wider tiles re-read less of A and W from L2 per flop; narrow ones waste less on small N.
     if (N > 128 && (long long)((M + 127) / 128) * ((N + 255) / 256) >= 96)
         return launch_tc<256, 4>(a, w, out, M, N, K, mode, flag, stream);

@@ -391,7 +391,9 @@ static int launch_linear(const void* a, const void* w, void* out, int M, int N, 
         return fail("skv_linear(bfloat16)", "operands must be 16-byte aligned");
     if ((norm.row_scale || norm.partials_in || norm.partials) && M > 64)
         return fail("skv_linear(bfloat16)", "the norm-fused form serves steps of at most 64 tokens");
-    if (M > 64 && tcgen05_enabled()) return linear_tcgen05(a, w, out, M, N, K, mode, flag, stream);
+    // above 16 tokens the tensor-memory kernels take over, unless a norm is folded into this projection
+    if (M > 16 && !norm.row_scale && !norm.partials_in && !norm.partials && tcgen05_enabled())
+        return linear_tcgen05(a, w, out, M, N, K, mode, flag, stream);
     // at most 8 warps and under 100 registers a thread: two blocks fit on an SM, so the next
     // kernel's weight loads are in flight while this one finishes
     if (M <= 8) return launch_skinny<1, 8, 16>(a, w, out, M, N, K, mode, act, norm, stream);

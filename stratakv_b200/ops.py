@@ -12,7 +12,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from .csrc.build import BuildError, build_library
-from .residual import COLUMNS_PER_PARTIAL, MAX_FUSED_ROWS, NormedRows
+from .residual import COLUMNS_PER_PARTIAL, KERNEL_FOLD_ROWS, NormedRows
 
 MODE_STORE, MODE_STORE_F32, MODE_ADD_F32, MODE_GATED = 0, 1, 2, 3
 ACTIVATIONS = {"silu": 0, "swish": 0}
@@ -111,7 +111,7 @@ class Kernels:
     def _fold_target(self, stats, rows: int, width: int):
         """Arguments (scaled rows, next norm's weight, partial sums, their stride, rows' factors, next norm's
         eps, counter) for a kernel that writes ``rows`` rows of the stream; None where it cannot fold."""
-        if stats is None or stats.next_norm is None or self.dtype != torch.bfloat16 or rows > MAX_FUSED_ROWS:
+        if stats is None or stats.next_norm is None or self.dtype != torch.bfloat16 or rows > KERNEL_FOLD_ROWS:
             return None
         gamma = stats.next_norm.gamma
         self._want(gamma, torch.float32, "gamma"); self._want(stats.partials, torch.float32, "partials")

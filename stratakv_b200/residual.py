@@ -28,8 +28,9 @@ from typing import Any, Optional
 
 import torch
 
-MAX_FUSED_ROWS = 64        # the small-batch projection kernel serves at most this many tokens
-CONSUMER_SUMS_ROWS = 16    # up to here the consumer adds the partial sums up, beyond the writer does
+KERNEL_FOLD_ROWS = 64      # the small-step projection kernel folds norms for at most this many tokens
+MAX_FUSED_ROWS = 16        # the engine asks for it up to here: larger steps run on the tensor-memory kernels, which do not fold
+CONSUMER_SUMS_ROWS = 16    # up to here the consumer adds the partial sums up, beyond (up to 64 rows) the writer does
 COLUMNS_PER_PARTIAL = 16   # a residual-add projection sums squares over 16 columns per block
 
 

@@ -61,7 +61,8 @@ def pack_gate_up(w):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,N,K", [(1, 48, 64), (3, 331, 80), (8, 256, 2048), (9, 100, 264), (17, 96, 96),
-                                   (33, 80, 176), (64, 512, 512), (70, 130, 520), (200, 64, 72)])
+                                   (33, 80, 176), (64, 512, 512), (70, 130, 520), (200, 64, 72),
+                                   (32, 2048, 5632), (64, 2560, 2048), (100, 1000, 1032), (128, 384, 4096)])
 def test_linear_store_and_add(dtype, M, N, K):
     from stratakv_b200 import ops
     k = lib(dtype)
@@ -85,7 +86,8 @@ def test_linear_store_and_add(dtype, M, N, K):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M,F,K", [(1, 176, 64), (5, 104, 80), (8, 5632, 2048), (40, 256, 96), (130, 24, 72)])
+@pytest.mark.parametrize("M,F,K", [(1, 176, 64), (5, 104, 80), (8, 5632, 2048), (40, 256, 96), (130, 24, 72),
+                                   (24, 72, 264), (64, 5632, 2048), (128, 200, 520)])
 def test_linear_gated(dtype, M, F, K):
     from stratakv_b200 import ops
     k = lib(dtype)
@@ -189,7 +191,11 @@ def test_linear_with_folded_norm(M, N, K, hidden_out):
         k.linear(a, w_add, plain, ops.MODE_ADD_F32)
         stats.expect(norm_b)
         k.linear(a, w_add, x, ops.MODE_ADD_F32, stats=stats)
-        assert torch.equal(x, plain)                                     # the sum itself is unchanged
+        if M <= 16:
+            assert torch.equal(x, plain)                                 # the same kernel: the sum itself is unchanged
+        else:                                                            # above 16 tokens the plain call is another kernel
+            slack = 2e-6 * (1 + a.double().abs() @ w_add.double().abs().T) + 1e-6 * plain.double().abs()
+            assert ((x.double() - plain.double()).abs() <= slack).all()
         assert stats.ready_for(norm_b)
         check(norm_b)
     # 3. a gated projection takes the folded norm too
