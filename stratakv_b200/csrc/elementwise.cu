@@ -256,7 +256,8 @@ SKV_EXPORT int skv_rmsnorm(const float* x, const float* gamma, float eps, void* 
                            int n_rows, int hidden, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (hidden <= 0) return fail("skv_rmsnorm", "hidden must be positive");
-    if (n_rows >= 64 && hidden % 4 == 0 && (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out) & 15) == 0)
+    // a warp per row once there are rows enough to fill the GPU that way, else a block per row
+    if (n_rows >= 1024 && hidden % 4 == 0 && (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out) & 15) == 0)
         return launch_pdl("skv_rmsnorm", rmsnorm_rows_kernel<skv_t>, dim3((n_rows + 7) / 8), dim3(256), 0, stream, x,
                           gamma, eps, (skv_t*)out, rows, n_rows, hidden);
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);

@@ -492,8 +492,16 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const int row = quarter * 32 + lane;          // weight row within the tile = TMEM lane
     const int n = n0 + row;
     bool ok = true;
+    // In the residual-add mode the first 64 tokens' old values are fetched while the main loop runs.
+    constexpr int EARLY = MP < 64 ? MP : 64;
+    float early[EARLY];
     if (warp >= 2) {
         pdl_wait();                               // the residual stream that the epilogue reads is the kernels' before
+        if (mode == TC_MODE_ADD_F32 && split == 0) {
+#pragma unroll
+            for (int j = 0; j < EARLY; ++j)
+                early[j] = (j < M && n < N) ? __ldcg((const float*)out + (size_t)j * N + n) : 0.0f;
+        }
         ok = k_iters == 0 || mbar_wait(acc_full, 0, flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
@@ -530,8 +538,9 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     if (warp >= 2 && split == 0) {
-#pragma unroll 1
-        for (int c = 0; c < MP && c < M; c += 32) {
+#pragma unroll
+        for (int c = 0; c < MP; c += 32) {
+            if (c >= M) break;
             uint32_t v[32];
             read_accumulator(c, v);
             for (int r = 1; r < splits; ++r) {    // rank order: the sum does not depend on timing
@@ -561,8 +570,13 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
                         if (c + j < M) ((float*)out)[(size_t)(c + j) * N + n] = __uint_as_float(v[j]);
                 } else {
                     float old[32];
+                    if (c < EARLY) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) old[j] = c + j < M ? __ldcg((const float*)out + (size_t)(c + j) * N + n) : 0.0f;
+                        for (int j = 0; j < 32; ++j) old[j] = early[(c < EARLY ? c : 0) + j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) old[j] = c + j < M ? __ldcg((const float*)out + (size_t)(c + j) * N + n) : 0.0f;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (c + j < M) ((float*)out)[(size_t)(c + j) * N + n] = old[j] + __uint_as_float(v[j]);
