@@ -713,11 +713,12 @@ static int launch_few_tokens(const void* a, const void* w, void* out, int M, int
         if (status != cudaSuccess) return fail("skv_linear(tcgen05)", cudaGetErrorString(status));
         sm_count = count;
     }
-    // Parts of K per tile of 128 weight rows: the largest power of two that keeps the grid within the GPU, leaves
+    // Parts of K per tile of 128 weight rows: the largest power of two up to 4 (eight ranks pushing into one block
+    // measured slower than four) that keeps the grid within the GPU, leaves
     // every part at least four 64-wide steps, and whose partial results fit where the pipeline's stages were.
     const int n_tiles = (N + 127) / 128, k_blocks = (K + TC_BK - 1) / TC_BK;
     int splits = 1;
-    while (splits < 8 && n_tiles * splits * 2 <= sm_count && k_blocks >= splits * 2 * 4 &&
+    while (splits < 4 && n_tiles * splits * 2 <= sm_count && k_blocks >= splits * 2 * 4 &&
            (size_t)(splits * 2 - 1) * MP * 128 * 4 <= ring)
         splits *= 2;
     cudaLaunchConfig_t config = {};
