@@ -26,14 +26,15 @@ def decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148
     return max(1, min(by_length, by_count, 64))
 
 
-def fused_decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148) -> int:
+def fused_decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148, per_sm: int = 2) -> int:
     """The same for the fused kernel, whose pieces are the blocks of one cluster: the largest
     power of two (other cluster sizes measured slower), at most 8, that keeps the grid within
-    two blocks per SM.  Half as many if that gives every block an SM to itself and a piece of
-    at most 512 keys, which such a block fetches whole before its inputs are ready."""
+    ``per_sm`` blocks per SM (2 up to head size 64, 1 above: the staged keys of a block take
+    shared memory in proportion).  Half as many if that gives every block an SM to itself and
+    a piece of at most 512 keys, which such a block fetches whole before its inputs are ready."""
     pairs = max(1, n_seqs * blocks_per_seq)
     by_length = max(1, max_ctx // 128)
-    wanted = max(1, min(by_length, 2 * sms // pairs, 8))
+    wanted = max(1, min(by_length, per_sm * sms // pairs, 8))
     wanted = 1 << (wanted.bit_length() - 1)
     if wanted > 1 and pairs * wanted > sms >= pairs * wanted // 2 and max_ctx * 2 <= 512 * wanted:
         wanted //= 2
@@ -92,7 +93,7 @@ class PagedAttention(Mixer):
         blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
         if step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table"):
             # one kernel: rotation, cache write, attention over the context in up to 8 pieces, merge
-            splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx)
+            splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx, per_sm=2 if s.head_dim <= 64 else 1)
             ops.attention_decode_fused(qkv, self.position.fusion_table(step.max_ctx), k_cache, v_cache, table,
                                        step.ctx_after, ctx, s.num_heads, s.num_kv_heads, s.head_dim,
                                        step.cache.block_size, s.scale, s.window, splits, writes_cache)
