@@ -138,8 +138,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto bar = [&](int which, int index = 0) { return bar0 + 8u * (uint32_t)(which + index); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int seq = blockIdx.x / tiles_per_seq, tile = blockIdx.x - seq * tiles_per_seq;
-    const int head = blockIdx.y;
+    // Heads run fastest (the heads of a KV head work on the same keys at the same time), and the query tiles
+    // are handed out last first: under a causal mask the last tile of a prompt has the most keys, and the
+    // blocks that start when the first ones have left should be the short ones.
+    const int order = (int)(gridDim.y - 1 - blockIdx.y);
+    const int seq = order / tiles_per_seq, tile = order - seq * tiles_per_seq;
+    const int head = blockIdx.x;
     const int kv_head = head / (num_heads / num_kv_heads);
     pdl_launch_dependents();
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
@@ -435,7 +439,7 @@ SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, cons
     if (int code = a_map(v_cache, cache_rows, AHD, rows_per_load, &map_v)) return code;
     const int tiles_per_seq = (max_q_len + ABM - 1) / ABM;
     const long long blocks = (long long)n_seqs * tiles_per_seq;
-    if (blocks > 0x7fffffffLL || num_heads > 65535) return fail("skv_attention_prefill_tc", "too many tokens or heads");
+    if (blocks > 65535) return fail("skv_attention_prefill_tc", "too many query tiles in one step (65,535 at most)");
     const size_t smem = (size_t)(ACH + 2) * TILE_BYTES + (size_t)4 * ACH * KV_TILE_BYTES + B_COUNT * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
@@ -444,7 +448,7 @@ SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, cons
         if (status != cudaSuccess) return fail("skv_attention_prefill_tc", cudaGetErrorString(status));
         configured = true;
     }
-    return launch_pdl("skv_attention_prefill_tc", prefill_attention_tc_kernel, dim3((unsigned)blocks, num_heads),
+    return launch_pdl("skv_attention_prefill_tc", prefill_attention_tc_kernel, dim3(num_heads, (unsigned)blocks),
                       dim3(ATHREADS), smem, stream, map_q, map_k, map_v, block_table, table_width, cu_q, ctx_after,
                       (__nv_bfloat16*)out, num_heads, num_kv_heads, block_size, rows_per_load, scale, window,
                       tiles_per_seq, flag);

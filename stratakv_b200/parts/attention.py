@@ -111,7 +111,8 @@ class PagedAttention(Mixer):
             ops.attention_decode(q, k_cache, v_cache, table, step.ctx_after, ctx, s.num_heads, s.num_kv_heads,
                                  s.head_dim, step.cache.block_size, s.scale, s.window, splits, scratch_o, scratch_ml)
         elif (rt.dtype == torch.bfloat16 and ops.has_attention_prefill_tc() and step.max_q_len > 32
-              and step.cache.block_size & (step.cache.block_size - 1) == 0):
+              and step.cache.block_size & (step.cache.block_size - 1) == 0
+              and step.n_seqs * -(-step.max_q_len // 128) <= 65535):
             ops.attention_prefill_tc(q, k_cache, v_cache, table, step.cu_q, step.ctx_after, ctx, step.max_q_len,
                                      s.num_heads, s.num_kv_heads, s.head_dim, step.cache.block_size, s.scale, s.window)
         elif rt.dtype == torch.bfloat16 and ops.has_attention_prefill():
