@@ -187,16 +187,22 @@ def time_e2e(engine, batch, start_context, steps, vocab):
 def time_prefill(engine, tokens, vocab, repeats=3):
     import torch
     from stratakv_b200 import StepEntry
+    import gc
     times = []
     for repeat in range(repeats + 1):
         slot = engine.open_sequence()
         ids = random_ids(tokens, vocab, 3000 + repeat)
-        torch.cuda.synchronize()
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        begin.record()
-        engine.step([StepEntry(slot, ids, [tokens - 1])])
-        end.record()
-        torch.cuda.synchronize()
+        gc.collect()                                  # a collection of the generation runs' garbage inside the
+        gc.disable()                                  # timed step would be host noise, not the step's time
+        try:
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            engine.step([StepEntry(slot, ids, [tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+        finally:
+            gc.enable()
         engine.close_sequence(slot)
         if repeat:                                    # the first run is the warm-up
             times.append(begin.elapsed_time(end))

@@ -13,6 +13,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import models as _models  # noqa: F401  (registers the architectures)
@@ -116,19 +117,23 @@ class Engine:
             raise StepError("a sequence appears twice in one step")
         if len(entries) > self.config.slots:
             raise StepError(f"{len(entries)} sequences in one step; the engine holds {self.config.slots}")
-        q_lens, ctx_before, wanted = [], [], {}
+        q_lens, ctx_before, wanted, token_arrays = [], [], {}, []
         for e in entries:
             if e.slot not in self.cache.sequences:
                 raise StepError(f"slot {e.slot} is not open")
             if len(e.tokens) == 0:
                 raise StepError(f"slot {e.slot}: a step needs at least one token per sequence")
-            for token in e.tokens:
-                if not (0 <= int(token) < vocab):
-                    raise StepError(f"slot {e.slot}: token id {token} is outside the vocabulary of {vocab}")
+            tokens = np.asarray(e.tokens)
+            if tokens.dtype.kind not in "iu":
+                tokens = np.array([int(t) for t in e.tokens], dtype=np.int64)
+            outside = np.flatnonzero((tokens < 0) | (tokens >= vocab))
+            if outside.size:
+                raise StepError(f"slot {e.slot}: token id {int(tokens[outside[0]])} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside this step's {len(e.tokens)} tokens")
             before = self.cache.length(e.slot)
+            token_arrays.append(tokens)
             q_lens.append(len(e.tokens))
             ctx_before.append(before)
             wanted[e.slot] = before + len(e.tokens)
@@ -137,32 +142,37 @@ class Engine:
         n, total = len(entries), sum(q_lens)
         max_ctx = max(wanted.values())
         width = -(-max_ctx // self.cache.block_size)
-        token_ids, positions, token_seq, want_rows, cu_q = [], [], [], [], [0]
-        for index, e in enumerate(entries):
-            base = cu_q[-1]
-            token_ids.extend(int(t) for t in e.tokens)
-            positions.extend(range(ctx_before[index], ctx_before[index] + q_lens[index]))
-            token_seq.extend([index] * q_lens[index])
-            want_rows.extend(base + int(w) for w in e.want)
-            cu_q.append(base + q_lens[index])
-        ctx_after = [wanted[s] for s in slots]
+        cu_q = np.zeros(n + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=cu_q[1:])
+        want_rows = [int(cu_q[index]) + int(w) for index, e in enumerate(entries) for w in e.want]
         tables = [self.cache.block_table_rows(g.index, slots, width) for g in self.cache.groups]
-        flat: List[int] = []
-        offsets = {}
-        for name, values in (("token_ids", token_ids), ("positions", positions), ("token_seq", token_seq),
-                             ("cu_q", cu_q), ("ctx_after", ctx_after), ("slot_ids", slots),
-                             ("want_rows", want_rows)):
-            offsets[name] = (len(flat), len(values))
-            flat.extend(values)
-        for g, rows in enumerate(tables):
-            offsets[("table", g)] = (len(flat), n * width)
-            for row in rows:
-                flat.extend(row)
-        pinned, meta = self._metadata(len(flat))
+        # everything goes into one pinned array, written through its numpy view, and up in one copy
+        pieces = (("token_ids", total), ("positions", total), ("token_seq", total), ("cu_q", n + 1), ("ctx_after", n),
+                  ("slot_ids", n), ("want_rows", len(want_rows))) + tuple((("table", g), n * width) for g in range(len(tables)))
+        offsets, length = {}, 0
+        for name, count in pieces:
+            offsets[name] = (length, count)
+            length += count
+        pinned, meta = self._metadata(length)
         if self._copied is not None:
             self._copied.synchronize()          # the last step's copy must have left the pinned array
-        pinned[:len(flat)] = torch.tensor(flat, dtype=torch.int32)
-        meta[:len(flat)].copy_(pinned[:len(flat)], non_blocking=True)
+        host = pinned.numpy()
+
+        def put(key, values):
+            start, count = offsets[key]
+            host[start:start + count] = values
+
+        put("token_ids", np.concatenate(token_arrays) if n > 1 else token_arrays[0])
+        put("positions", np.concatenate([np.arange(b, b + q) for b, q in zip(ctx_before, q_lens)]))
+        put("token_seq", np.repeat(np.arange(n), q_lens))
+        put("cu_q", cu_q)
+        put("ctx_after", [wanted[slot] for slot in slots])
+        put("slot_ids", slots)
+        if want_rows:
+            put("want_rows", want_rows)
+        for g, rows in enumerate(tables):
+            put(("table", g), np.asarray(rows, dtype=np.int64).reshape(-1))
+        meta[:length].copy_(pinned[:length], non_blocking=True)
         if self.device.type == "cuda":
             self._copied = self._copied or torch.cuda.Event()
             self._copied.record()
