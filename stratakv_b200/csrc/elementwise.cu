@@ -86,8 +86,20 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma
     const int src = rows ? rows[r] : r;
     const float4* row = (const float4*)(x + (size_t)src * hidden);
     const int quads = hidden >> 2;
+    // The first 2,048 columns of the row stay in registers: all their loads are in flight at once and nothing of
+    // them is read again.  A longer row's remainder is read twice, as the whole row was before.
+    constexpr int HELD = 16;
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 held[HELD];
+#pragma unroll
+    for (int j = 0; j < HELD; ++j) held[j] = lane + 32 * j < quads ? row[lane + 32 * j] : zero;
     float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int i = lane; i < quads; i += 32) {
+#pragma unroll
+    for (int j = 0; j < HELD; ++j) {
+        partial[0] = fmaf(held[j].x, held[j].x, partial[0]); partial[1] = fmaf(held[j].y, held[j].y, partial[1]);
+        partial[2] = fmaf(held[j].z, held[j].z, partial[2]); partial[3] = fmaf(held[j].w, held[j].w, partial[3]);
+    }
+    for (int i = lane + 32 * HELD; i < quads; i += 32) {
         const float4 v = row[i];
         partial[0] = fmaf(v.x, v.x, partial[0]); partial[1] = fmaf(v.y, v.y, partial[1]);
         partial[2] = fmaf(v.z, v.z, partial[2]); partial[3] = fmaf(v.w, v.w, partial[3]);
@@ -96,8 +108,8 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma
     const float inverse_rms = 1.0f / sqrtf(mean_square + eps);
     T* row_out = out + (size_t)r * hidden;
     const float4* g4 = (const float4*)gamma;
-    for (int i = lane; i < quads; i += 32) {
-        const float4 v = row[i], g = g4[i];
+    auto emit = [&](int i, const float4& v) {
+        const float4 g = g4[i];
         const float y0 = v.x * inverse_rms * g.x, y1 = v.y * inverse_rms * g.y;
         const float y2 = v.z * inverse_rms * g.z, y3 = v.w * inverse_rms * g.w;
         if (sizeof(T) == 4) {
@@ -106,7 +118,11 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gamma
             const __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
             ((uint2*)row_out)[i] = make_uint2(*(const uint32_t*)&lo, *(const uint32_t*)&hi);
         }
-    }
+    };
+#pragma unroll
+    for (int j = 0; j < HELD; ++j)
+        if (lane + 32 * j < quads) emit(lane + 32 * j, held[j]);
+    for (int i = lane + 32 * HELD; i < quads; i += 32) emit(i, row[i]);
 }
 
 // ---------------------------------------------------------------------------
@@ -182,10 +198,12 @@ rope_kv_write_vec_kernel(const float* __restrict__ qkv, const float2* __restrict
                          const int* __restrict__ positions, const int* __restrict__ token_seq,
                          const int* __restrict__ block_table, int table_width, T* __restrict__ q_out,
                          T* __restrict__ k_cache, T* __restrict__ v_cache, int num_heads, int num_kv_heads,
-                         int head_dim, int block_size, int write_kv) {
+                         int head_dim, int block_size, int write_kv, int n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
+    // a warp per token, four tokens per block: a grid of one small block per token takes longer to start than to run
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= n_tokens) return;
     const int half = head_dim >> 1, quads = half >> 2;
     const int q_dim = num_heads * head_dim, kv_dim = num_kv_heads * head_dim;
     const int pos = positions[t];
@@ -198,7 +216,7 @@ rope_kv_write_vec_kernel(const float* __restrict__ qkv, const float2* __restrict
         tile_base = ((size_t)block * num_kv_heads * block_size + (pos % block_size)) * head_dim;
     }
     const int rotary_heads = num_heads + (write_kv ? num_kv_heads : 0);
-    for (int idx = threadIdx.x; idx < rotary_heads * quads; idx += blockDim.x) {
+    for (int idx = lane; idx < rotary_heads * quads; idx += 32) {
         const int head = idx / quads, i = (idx - head * quads) << 2;
         const float* x = src + (size_t)head * head_dim;
         const float4 x1 = *(const float4*)(x + i), x2 = *(const float4*)(x + i + half);
@@ -217,7 +235,7 @@ rope_kv_write_vec_kernel(const float* __restrict__ qkv, const float2* __restrict
     }
     if (write_kv) {
         const float* v = src + q_dim + kv_dim;
-        for (int idx = threadIdx.x; idx < kv_dim >> 2; idx += blockDim.x) {
+        for (int idx = lane; idx < kv_dim >> 2; idx += 32) {
             const int e = idx << 2, g = e / head_dim, d = e - g * head_dim;
             const float4 value = *(const float4*)(v + e);
             store4<T>(v_cache + tile_base + (size_t)g * block_size * head_dim + d, value.x, value.y, value.z, value.w);
@@ -276,9 +294,10 @@ SKV_EXPORT int skv_rope_kv_write(const float* qkv, const float* cos_sin, const i
         return fail("skv_rope_kv_write", "head counts and block_size must be positive");
     if (head_dim % 8 == 0 && (((uintptr_t)qkv | (uintptr_t)cos_sin | (uintptr_t)q_out | (uintptr_t)k_cache |
                                (uintptr_t)v_cache) & 15) == 0)
-        return launch_pdl("skv_rope_kv_write", rope_kv_write_vec_kernel<skv_t>, dim3(n_tokens), dim3(128), 0, stream,
+        return launch_pdl("skv_rope_kv_write", rope_kv_write_vec_kernel<skv_t>, dim3((n_tokens + 3) / 4), dim3(128), 0, stream,
                           qkv, (const float2*)cos_sin, positions, token_seq, block_table, table_width, (skv_t*)q_out,
-                          (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv);
+                          (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv,
+                          n_tokens);
     return launch_pdl("skv_rope_kv_write", rope_kv_write_kernel<skv_t>, dim3(n_tokens), dim3(128), 0, stream, qkv,
                       (const float2*)cos_sin, positions, token_seq, block_table, table_width, (skv_t*)q_out,
                       (skv_t*)k_cache, (skv_t*)v_cache, num_heads, num_kv_heads, head_dim, block_size, write_kv);
