@@ -216,22 +216,40 @@ rope_kv_write_vec_kernel(const float* __restrict__ qkv, const float2* __restrict
         tile_base = ((size_t)block * num_kv_heads * block_size + (pos % block_size)) * head_dim;
     }
     const int rotary_heads = num_heads + (write_kv ? num_kv_heads : 0);
-    for (int idx = lane; idx < rotary_heads * quads; idx += 32) {
-        const int head = idx / quads, i = (idx - head * quads) << 2;
-        const float* x = src + (size_t)head * head_dim;
-        const float4 x1 = *(const float4*)(x + i), x2 = *(const float4*)(x + i + half);
-        float4 c = make_float4(1.0f, 1.0f, 1.0f, 1.0f), s = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (angles) {
-            const float4 a = angles[i >> 1], b = angles[(i >> 1) + 1];      // (cos, sin) pairs i..i+1 and i+2..i+3
-            c = make_float4(a.x, a.z, b.x, b.z);
-            s = make_float4(a.y, a.w, b.y, b.w);
+    // four items per lane and round: their loads go out together, then the four are rotated and stored
+    const int items = rotary_heads * quads;
+    for (int first = lane; first < items; first += 128) {
+        float4 x1[4], x2[4], c[4], sn[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int idx = first + 32 * u;
+            if (idx < items) {
+                const int head = idx / quads, i = (idx - head * quads) << 2;
+                const float* x = src + (size_t)head * head_dim;
+                x1[u] = *(const float4*)(x + i);
+                x2[u] = *(const float4*)(x + i + half);
+                c[u] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                sn[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (angles) {
+                    const float4 a = angles[i >> 1], b = angles[(i >> 1) + 1];      // (cos, sin) pairs i..i+1 and i+2..i+3
+                    c[u] = make_float4(a.x, a.z, b.x, b.z);
+                    sn[u] = make_float4(a.y, a.w, b.y, b.w);
+                }
+            }
         }
-        T* dst = head < num_heads ? q_out + (size_t)t * q_dim + (size_t)head * head_dim
-                                  : k_cache + tile_base + (size_t)(head - num_heads) * block_size * head_dim;
-        store4<T>(dst + i, x1.x * c.x - x2.x * s.x, x1.y * c.y - x2.y * s.y, x1.z * c.z - x2.z * s.z,
-                  x1.w * c.w - x2.w * s.w);
-        store4<T>(dst + i + half, x1.x * s.x + x2.x * c.x, x1.y * s.y + x2.y * c.y, x1.z * s.z + x2.z * c.z,
-                  x1.w * s.w + x2.w * c.w);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int idx = first + 32 * u;
+            if (idx < items) {
+                const int head = idx / quads, i = (idx - head * quads) << 2;
+                T* dst = head < num_heads ? q_out + (size_t)t * q_dim + (size_t)head * head_dim
+                                          : k_cache + tile_base + (size_t)(head - num_heads) * block_size * head_dim;
+                store4<T>(dst + i, x1[u].x * c[u].x - x2[u].x * sn[u].x, x1[u].y * c[u].y - x2[u].y * sn[u].y,
+                          x1[u].z * c[u].z - x2[u].z * sn[u].z, x1[u].w * c[u].w - x2[u].w * sn[u].w);
+                store4<T>(dst + i + half, x1[u].x * sn[u].x + x2[u].x * c[u].x, x1[u].y * sn[u].y + x2[u].y * c[u].y,
+                          x1[u].z * sn[u].z + x2[u].z * c[u].z, x1[u].w * sn[u].w + x2[u].w * c[u].w);
+            }
+        }
     }
     if (write_kv) {
         const float* v = src + q_dim + kv_dim;
