@@ -526,6 +526,7 @@ def test_attention_prefill_at_the_edges_of_tiles_and_windows():
     (20, 1, 32, 16, [90, 45], 0, 4, True),                 # more than 16 query heads on one KV head
     (4, 2, 32, 16, [90, 45, 7], 20, 2, True),              # a window
     (8, 2, 80, 64, [500, 16, 17], 0, 8, False),            # no rotation; more splits than work for some
+    (2, 1, 32, 16, [9000, 300], 0, 4, True),               # a block table longer than the kernel keeps in shared memory
 ])
 def test_attention_decode_fused_equals_the_separate_kernels(heads, kv_heads, head_dim, block_size, lengths, window,
                                                             splits, rotate):
@@ -538,7 +539,7 @@ def test_attention_decode_fused_equals_the_separate_kernels(heads, kv_heads, hea
     setup = paged_setup(dtype, lengths, [1] * n, heads, kv_heads, head_dim, block_size, seed=heads * 7 + head_dim)
     g = torch.Generator().manual_seed(99)
     qkv = torch.randn(n, (heads + 2 * kv_heads) * head_dim, generator=g).cuda()
-    table = torch.from_numpy(rope_table(head_dim, 5000.0, 2048)).cuda() if rotate else None
+    table = torch.from_numpy(rope_table(head_dim, 5000.0, max(2048, max(lengths) + 8))).cuda() if rotate else None
     ctx_after = torch.tensor(lengths, dtype=torch.int32, device="cuda")
     scale = 0.5 / math.sqrt(head_dim)
     # the separate kernels
