@@ -171,7 +171,7 @@ struct NormArgs {
 // Weights do not depend on the kernel before this one, so the first batch of
 // weight loads is issued before pdl_wait(): it overlaps the predecessor's tail.
 template <int TG, int U, bool STREAM, int MAX_WARPS>
-__global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS == 4 ? (TG == 1 ? 5 : (TG == 2 ? 4 : 2)) : (MAX_WARPS == 8 && TG <= 2 ? 2 : 1))
+__global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS == 4 ? (TG == 1 ? 5 : (TG == 2 ? 5 : 2)) : (MAX_WARPS == 8 && TG <= 2 ? 2 : 1))
 skinny_linear_bf16_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                           void* __restrict__ out, int M, int N, int K, int mode, int act, const NormArgs norm) {
     extern __shared__ float red[];                 // [warps][16][8*TG + 1], [8*TG] factors, [8*TG][n_partials_in] partial sums
