@@ -91,9 +91,15 @@ class PagedAttention(Mixer):
         table = step.block_tables[step.cache.entry_group_index(cache_entry)]
         ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
         blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
-        if step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table"):
-            # one kernel: rotation, cache write, attention over the context in up to 8 pieces, merge
+        fused = step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table")
+        if fused:
             splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx, per_sm=2 if s.head_dim <= 64 else 1)
+            # A cluster holds at most 8 pieces.  Few long sequences want more (batch 1 at 32,000 keys: 64 pieces
+            # through scratch memory and a combine kernel take 1.14 ms a step, 8 pieces in the cluster 1.72 ms).
+            if step.max_ctx >= 2048 * splits and decode_splits(n, blocks_per_seq, step.max_ctx) >= 2 * splits:
+                fused = False
+        if fused:
+            # one kernel: rotation, cache write, attention over the context in up to 8 pieces, merge
             ops.attention_decode_fused(qkv, self.position.fusion_table(step.max_ctx), k_cache, v_cache, table,
                                        step.ctx_after, ctx, s.num_heads, s.num_kv_heads, s.head_dim,
                                        step.cache.block_size, s.scale, s.window, splits, writes_cache)
