@@ -96,7 +96,8 @@ class PagedAttention(Mixer):
             splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx, per_sm=2 if s.head_dim <= 64 else 1)
             # A cluster holds at most 8 pieces.  Few long sequences want more (batch 1 at 32,000 keys: 64 pieces
             # through scratch memory and a combine kernel take 1.14 ms a step, 8 pieces in the cluster 1.72 ms).
-            if step.max_ctx >= 2048 * splits and decode_splits(n, blocks_per_seq, step.max_ctx) >= 2 * splits:
+            if (n * blocks_per_seq * splits < 148 and step.max_ctx >= 2048 * splits
+                    and decode_splits(n, blocks_per_seq, step.max_ctx) >= 2 * splits):
                 fused = False
         if fused:
             # one kernel: rotation, cache write, attention over the context in up to 8 pieces, merge
