@@ -41,6 +41,15 @@ def fused_decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int
     return wanted
 
 
+def wants_more_pieces(n_seqs: int, blocks_per_seq: int, max_ctx: int, cluster_splits: int, sms: int = 148) -> bool:
+    """A cluster holds at most 8 pieces of a context.  Few long sequences want more: when the fused kernel's
+    grid leaves SMs idle, its pieces are 2,048 keys or longer and the path through scratch memory would cut
+    at least twice as many (batch 1 at 32,000 keys: 1.14 ms a step with 64 pieces and a combine kernel,
+    1.72 ms with 8 pieces in one cluster)."""
+    return (n_seqs * blocks_per_seq * cluster_splits < sms and max_ctx >= 2048 * cluster_splits
+            and decode_splits(n_seqs, blocks_per_seq, max_ctx, sms) >= 2 * cluster_splits)
+
+
 class PagedAttention(Mixer):
     graph_safe = True
     folds_norm = True
@@ -94,11 +103,7 @@ class PagedAttention(Mixer):
         fused = step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table")
         if fused:
             splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx, per_sm=2 if s.head_dim <= 64 else 1)
-            # A cluster holds at most 8 pieces.  Few long sequences want more (batch 1 at 32,000 keys: 64 pieces
-            # through scratch memory and a combine kernel take 1.14 ms a step, 8 pieces in the cluster 1.72 ms).
-            if (n * blocks_per_seq * splits < 148 and step.max_ctx >= 2048 * splits
-                    and decode_splits(n, blocks_per_seq, step.max_ctx) >= 2 * splits):
-                fused = False
+            fused = not wants_more_pieces(n, blocks_per_seq, step.max_ctx, splits)
         if fused:
             # one kernel: rotation, cache write, attention over the context in up to 8 pieces, merge
             ops.attention_decode_fused(qkv, self.position.fusion_table(step.max_ctx), k_cache, v_cache, table,

@@ -4,7 +4,7 @@ from types import SimpleNamespace
 
 import torch
 
-from stratakv_b200.parts.attention import decode_splits, fused_decode_splits
+from stratakv_b200.parts.attention import decode_splits, fused_decode_splits, wants_more_pieces
 from stratakv_b200.parts.block import foldable, pre_norm
 from stratakv_b200.residual import NormedRows, ResidualStats
 
@@ -105,3 +105,12 @@ def test_context_splits_depend_on_sizes_only():
                 assert 1 <= plain <= 64 and plain * 128 <= max(ctx, 128)
     assert fused_decode_splits(8, 4, 2048) == 4 and fused_decode_splits(8, 4, 4096) == 8
     assert fused_decode_splits(64, 4, 2048) == 1 and fused_decode_splits(1, 4, 2048) == 8
+
+
+def test_only_few_long_sequences_leave_the_cluster_kernel():
+    def leaves(batch, groups, ctx, per_sm=2):
+        return wants_more_pieces(batch, groups, ctx, fused_decode_splits(batch, groups, ctx, per_sm=per_sm))
+    assert leaves(1, 4, 32768) and leaves(2, 4, 32768)
+    assert not leaves(1, 4, 8192) and not leaves(8, 4, 2048) and not leaves(8, 4, 16384)
+    assert not leaves(8, 32, 2048, per_sm=1)              # many heads fill the GPU with one piece each
+    assert not leaves(64, 4, 32768)
