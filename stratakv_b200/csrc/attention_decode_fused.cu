@@ -33,16 +33,24 @@ constexpr int FKSTEPS = FHD / 16, FOTILES = FHD / 8;
 constexpr int FWARPS = 8, FTHREADS = FWARPS * 32;
 constexpr int FCHUNK = FWARPS * 16;                 // keys per stage: one group of 16 per warp
 constexpr int FMAX_STAGES = 4;                      // stages per launch: 2 .. FMAX_STAGES (see the launch below)
-constexpr int FROW = FHD * 2 + 16;                  // bytes between staged rows: ldmatrix reads 8 rows without bank conflicts
+// Staged rows: ldmatrix reads 16 bytes of each of 8 neighbouring rows at once, which must fall on different banks.
+// Rows of whole 128-byte multiples are stored with their 16-byte pieces exchanged (piece ^ (row & 7)), at no cost
+// in space; other head sizes get 16 bytes of padding per row.
+constexpr bool FSWIZZLED = (FHD * 2) % 128 == 0;
+constexpr int FROW = FSWIZZLED ? FHD * 2 : FHD * 2 + 16;
+constexpr int FQROW = FHD * 2 + 16;                 // bytes between rows of the query tile and the new rows (padded)
+__device__ __forceinline__ uint32_t f_staged(int row, int piece) {          // byte offset of a row's 16-byte piece in a stage
+    return (uint32_t)(row * FROW + ((FSWIZZLED ? piece ^ (row & 7) : piece) << 4));
+}
 constexpr int FPIECES = FHD / 8;                    // 16-byte pieces per row
 constexpr int FSTAGE_BYTES = 2 * FCHUNK * FROW;     // keys, then values
 constexpr int FPITCH = FHD + 2;                     // floats per partial row: outputs, max, sum
 constexpr int FINBOX_ROWS = 24;                     // >= ceil(16 / blocks) * blocks for 1..8 blocks
 
 // shared memory, in bytes from the start
-constexpr int F_Q_AT = 0;                                           // [16][FROW] rotated queries
-constexpr int F_NEW_AT = F_Q_AT + 16 * FROW;                        // new key row, new value row
-constexpr int F_ANGLES_AT = F_NEW_AT + 2 * FROW;                    // [FHD/2] (cos, sin)
+constexpr int F_Q_AT = 0;                                           // [16][FQROW] rotated queries
+constexpr int F_NEW_AT = F_Q_AT + 16 * FQROW;                       // new key row, new value row
+constexpr int F_ANGLES_AT = F_NEW_AT + 2 * FQROW;                   // [FHD/2] (cos, sin)
 constexpr int F_INBOX_AT = F_ANGLES_AT + (FHD / 2) * 8;             // [FINBOX_ROWS][FPITCH] floats, written by the cluster
 constexpr int FTABLE = 512;                                         // entries of the block table kept in shared memory
 constexpr int F_TABLE_AT = F_INBOX_AT + FINBOX_ROWS * FPITCH * 4;   // [FTABLE] ints
@@ -172,7 +180,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                 size_t at = 0;
                 if (live)
                     at = ((size_t)(block_of(key) * num_kv_heads + kv_head) * block_size + row_in_block(key)) * FHD + piece * 8;
-                const uint32_t dst = stage + row * FROW + piece * 16;
+                const uint32_t dst = stage + f_staged(row, piece);
                 f_copy16(dst, k_cache + at, live ? 16 : 0);
                 f_copy16(dst + FCHUNK * FROW, v_cache + at, live ? 16 : 0);
             }
@@ -184,7 +192,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     for (int c = 0; c < stages; ++c) issue_chunk(c);
     if (threadIdx.x < HALF) angles[threadIdx.x] = my_angle;
     // query rows that no head fills stay zero
-    for (int i = threadIdx.x; i < 16 * FROW / 16; i += FTHREADS)
+    for (int i = threadIdx.x; i < 16 * FQROW / 16; i += FTHREADS)
         *(uint4*)(fused_smem + F_Q_AT + i * 16) = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
     pdl_wait();
@@ -211,7 +219,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
             }
             const uint2 low = make_uint2(f_pack(first[0], first[1]), f_pack(first[2], first[3]));
             const uint2 high = make_uint2(f_pack(second[0], second[1]), f_pack(second[2], second[3]));
-            unsigned char* row = item < rows ? fused_smem + F_Q_AT + item * FROW : fused_smem + F_NEW_AT;
+            unsigned char* row = item < rows ? fused_smem + F_Q_AT + item * FQROW : fused_smem + F_NEW_AT;
             *(uint2*)(row + 8 * quad) = low;
             *(uint2*)(row + 2 * HALF + 8 * quad) = high;
             if (item == rows) {
@@ -232,7 +240,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
                 } else {
                     packed = *(const uint2*)((which ? v_cache : k_cache) + new_at + 4 * quad);
                 }
-                *(uint2*)(fused_smem + F_NEW_AT + which * FROW + 8 * quad) = packed;
+                *(uint2*)(fused_smem + F_NEW_AT + which * FQROW + 8 * quad) = packed;
             }
         }
     }
@@ -242,7 +250,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
     uint32_t qa[FKSTEPS][4];
 #pragma unroll
     for (int s = 0; s < FKSTEPS; ++s)
-        f_ldmatrix(qa[s], smem + F_Q_AT + ((lane & 7) + ((lane >> 3) & 1) * 8) * FROW + (16 * s + (lane >> 4) * 8) * 2);
+        f_ldmatrix(qa[s], smem + F_Q_AT + ((lane & 7) + ((lane >> 3) & 1) * 8) * FQROW + (16 * s + (lane >> 4) * 8) * 2);
 
     float o[FOTILES][4];
 #pragma unroll
@@ -263,8 +271,8 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
             unsigned char* base = fused_smem + F_STAGES_AT + (c % stages) * FSTAGE_BYTES;
             for (int i = threadIdx.x; i < 2 * FPIECES; i += FTHREADS) {
                 const int which = i / FPIECES, piece = i - which * FPIECES;
-                *(uint4*)(base + which * FCHUNK * FROW + row * FROW + piece * 16) =
-                    *(const uint4*)(fused_smem + F_NEW_AT + which * FROW + piece * 16);
+                *(uint4*)(base + which * FCHUNK * FROW + f_staged(row, piece)) =
+                    *(const uint4*)(fused_smem + F_NEW_AT + which * FQROW + piece * 16);
             }
             __syncthreads();
         }
@@ -277,7 +285,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
 #pragma unroll
             for (int step = 0; step < FKSTEPS; ++step) {
                 uint32_t kb[4];                       // keys 0-7: dims 0-7, 8-15 of the step; keys 8-15 likewise
-                f_ldmatrix(kb, k_rows + ((lane & 7) + (lane >> 4) * 8) * FROW + (16 * step + ((lane >> 3) & 1) * 8) * 2);
+                f_ldmatrix(kb, k_rows + f_staged((lane & 7) + (lane >> 4) * 8, 2 * step + ((lane >> 3) & 1)));
                 f_mma(s[0], qa[step][0], qa[step][1], qa[step][2], qa[step][3], kb[0], kb[1]);
                 f_mma(s[1], qa[step][0], qa[step][1], qa[step][2], qa[step][3], kb[2], kb[3]);
             }
@@ -323,7 +331,7 @@ decode_attention_fused_kernel(const float* __restrict__ qkv, const float2* __res
 #pragma unroll
             for (int j = 0; j < FOTILES; j += 2) {
                 uint32_t vb[4];                       // dims 8j..: keys 0-7, 8-15; dims 8j+8..: keys 0-7, 8-15
-                f_ldmatrix_trans(vb, v_rows + ((lane & 7) + ((lane >> 3) & 1) * 8) * FROW + (8 * j + (lane >> 4) * 8) * 2);
+                f_ldmatrix_trans(vb, v_rows + f_staged((lane & 7) + ((lane >> 3) & 1) * 8, j + (lane >> 4)));
                 f_mma(o[j], a0, a1, a2, a3, vb[0], vb[1]);
                 f_mma(o[j + 1], a0, a1, a2, a3, vb[2], vb[3]);
             }
@@ -445,6 +453,8 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
     const long long blocks = (long long)n_seqs * num_kv_heads * m_tiles * splits;
     const long long piece_chunks = ((long long)table_width * block_size / splits + FCHUNK - 1) / FCHUNK;
     const int room = (F_SMEM_LIMIT - F_STAGES_AT) / FSTAGE_BYTES;
+    // (a third stage for longer pieces, which two blocks of head size 64 could still share an SM with, measured
+    // 7-12 % slower in the step at 8,100 and 16,200 keys)
     int stages = 2;
     if (blocks <= sm_count && piece_chunks <= FMAX_STAGES && piece_chunks <= room) stages = (int)(piece_chunks < 2 ? 2 : piece_chunks);
     const size_t smem = (size_t)F_STAGES_AT + (size_t)stages * FSTAGE_BYTES;
