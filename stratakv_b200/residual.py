@@ -62,8 +62,9 @@ class ResidualStats:
 
     @property
     def consumer_sums(self) -> bool:
-        # (the consumer stages rows x partial sums in shared memory: keep that within 32 KB)
-        return self.scaled.shape[0] <= CONSUMER_SUMS_ROWS and self.partials.shape[1] <= 512
+        # (the consumer stages rows x partial sums in shared memory beside its reduction area: 24 KB at most)
+        rows, width = self.partials.shape
+        return rows <= CONSUMER_SUMS_ROWS and rows * width <= 6144
 
     def filled(self, n_partials: int = 0) -> None:
         self.prepared_for = self.next_norm

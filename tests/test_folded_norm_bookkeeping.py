@@ -90,8 +90,10 @@ def test_statistics_are_for_one_norm_only():
 
 def test_few_rows_let_the_consumer_add_the_partial_sums():
     assert make_stats(rows=16).consumer_sums and not make_stats(rows=17).consumer_sums
-    wide = ResidualStats(torch.zeros(4, 64), torch.zeros(4), torch.zeros(4, 1024), torch.zeros(1, dtype=torch.int32))
+    wide = ResidualStats(torch.zeros(4, 64), torch.zeros(4), torch.zeros(4, 2048), torch.zeros(1, dtype=torch.int32))
     assert not wide.consumer_sums
+    assert ResidualStats(torch.zeros(8, 64), torch.zeros(8), torch.zeros(8, 512), torch.zeros(1, dtype=torch.int32)).consumer_sums
+    assert not ResidualStats(torch.zeros(16, 64), torch.zeros(16), torch.zeros(16, 512), torch.zeros(1, dtype=torch.int32)).consumer_sums
 
 
 def test_context_splits_depend_on_sizes_only():
