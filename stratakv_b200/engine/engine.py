@@ -289,14 +289,24 @@ class Engine:
         elif stop_ids is None:
             stop_ids = self.spec.stop_token_ids
 
+        on_gpu = self.device.type == "cuda"
+        landing = torch.empty(max(1, len(prompts)), dtype=torch.int32, pin_memory=on_gpu)   # chosen ids arrive here
+        landed = torch.cuda.Event() if on_gpu else None
+
         def choose(logits, row_streams, counters):
             if params.greedy:
                 tokens = sampler.sample(logits, None, None)
             else:
                 meta = torch.tensor([row_streams, counters], dtype=torch.int32).to(self.device)
                 tokens = sampler.sample(logits, meta[0], meta[1])
-            self._io_bytes = (self._io_bytes[0], tokens.numel() * 4)
-            return tokens.tolist()
+            count = tokens.numel()
+            self._io_bytes = (self._io_bytes[0], count * 4)
+            if not on_gpu:
+                return tokens.tolist()
+            landing[:count].copy_(tokens, non_blocking=True)
+            landed.record()
+            landed.synchronize()
+            return landing[:count].tolist()
 
         sync = torch.cuda.synchronize if self.device.type == "cuda" else (lambda: None)
         output = run(self, choose, prompts, max_new_tokens, stop_ids, streams, sync=sync)
