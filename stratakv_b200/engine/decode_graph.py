@@ -129,8 +129,13 @@ class DecodeGraph:
                     table[row, dropped:dropped + len(blocks)] = blocks
         self.staged = self._key(slots, ctx_before)
 
-    def fill(self, slots: Sequence[int], tokens: Sequence[int], ctx_before: Sequence[int]) -> None:
-        if self.staged is None or self.staged != self._key(slots, ctx_before):
+    def staged_for(self, slots: Sequence[int], ctx_before: Sequence[int]) -> bool:
+        """True if ``stage_rows`` has prepared exactly this step (these sequences at these lengths)."""
+        return self.staged is not None and self.staged == self._key(slots, ctx_before)
+
+    def fill(self, slots: Sequence[int], tokens: Sequence[int], ctx_before: Sequence[int], staged: bool = False) -> None:
+        """``staged``: the caller has checked ``staged_for`` for this step."""
+        if not staged:
             self.stage_rows(slots, ctx_before)
         self.staged = None
         live = len(slots)

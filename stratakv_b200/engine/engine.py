@@ -211,32 +211,35 @@ class Engine:
             raise StepError("a sequence appears twice in one step")
         if len(entries) > self.config.slots:
             raise StepError(f"{len(entries)} sequences in one step; the engine holds {self.config.slots}")
-        tokens, ctx_before, wanted, rows = [], [], {}, []
+        sequences = self.cache.sequences
+        try:
+            ctx_before = [sequences[slot].length for slot in slots]
+        except KeyError as missing:
+            raise StepError(f"slot {missing.args[0]} is not open") from None
+        tokens = [int(e.tokens[0]) for e in entries]
+        if min(tokens) < 0 or max(tokens) >= vocab:
+            slot, token = next((s, t) for s, t in zip(slots, tokens) if not (0 <= t < vocab))
+            raise StepError(f"slot {slot}: token id {token} is outside the vocabulary of {vocab}")
+        rows = []
         for index, e in enumerate(entries):
-            if e.slot not in self.cache.sequences:
-                raise StepError(f"slot {e.slot} is not open")
-            token = int(e.tokens[0])
-            if not (0 <= token < vocab):
-                raise StepError(f"slot {e.slot}: token id {token} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if int(w) != 0:
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside this step's 1 tokens")
                 rows.append(index)
-            before = self.cache.length(e.slot)
-            tokens.append(token)
-            ctx_before.append(before)
-            wanted[e.slot] = before + 1
-        self.cache.reserve(wanted)
-        need = -(-max(wanted.values()) // self.cache.block_size)
+        wanted = {slot: before + 1 for slot, before in zip(slots, ctx_before)}
         bucket = bucket_for(len(entries))
         graph = self._graphs.get(bucket)
-        if graph is None or graph.width < need:
-            width = 4
-            while width < need:
-                width *= 2
-            graph = DecodeGraph(self, bucket, width)
-            self._graphs[bucket] = graph
-        graph.fill(slots, tokens, ctx_before)
+        staged = graph is not None and graph.staged_for(slots, ctx_before)
+        if not staged:                          # (a staged step needs no new block and fits its graph: see _stage_next)
+            self.cache.reserve(wanted)
+            need = -(-max(wanted.values()) // self.cache.block_size)
+            if graph is None or graph.width < need:
+                width = 4
+                while width < need:
+                    width *= 2
+                graph = DecodeGraph(self, bucket, width)
+                self._graphs[bucket] = graph
+        graph.fill(slots, tokens, ctx_before, staged)
         logits = graph.run()
         self._io_bytes = (graph.host.numel() * 4, self._io_bytes[1])
         for slot, length in wanted.items():
