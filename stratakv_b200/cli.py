@@ -13,8 +13,11 @@ come from ``config.json``, where the reference guesses them from tensor shapes.
 Added here: ``--seed S`` (reproducible draws; the reference documents the flag
 but does not have it), ``--dtype bfloat16|float32``, ``--max-tokens N`` (cache
 size), ``--stop-id ID`` (repeatable; default: the model's eos ids),
-``--ignore-eos``, and ``--prompt-file FILE`` with one request per line, which
-are generated as a batch and printed one line each.
+``--ignore-eos``, ``--block-size N`` (cache block, default 64), ``--prompt-file FILE``
+with one request per line, which are generated as a batch and printed one line
+each, and ``--random CONFIG.json``: no checkpoint, weights drawn from
+``--weights-seed`` (default 0) for the configuration in that file; ``<model>`` is
+left out then.
 """
 from __future__ import annotations
 
@@ -26,7 +29,8 @@ from pathlib import Path
 from typing import List, Optional
 
 USAGE = ("Usage: stratakv_cli [--temp T] [--top-k K] [--top-p P] [--seed S] [--dtype bfloat16|float32]\n"
-         "                    [--max-tokens N] [--stop-id ID]... [--ignore-eos] [--prompt-file FILE]\n"
+         "                    [--max-tokens N] [--block-size N] [--stop-id ID]... [--ignore-eos]\n"
+         "                    [--prompt-file FILE] [--random CONFIG.json [--weights-seed S]]\n"
          "                    <model> <max_new_tokens> <prompt_id>...\n"
          "       options may also appear between max_new_tokens and the prompt tokens\n")
 
@@ -48,6 +52,9 @@ class Arguments:
     max_tokens: Optional[int] = None
     stop_ids: Optional[List[int]] = None
     ignore_eos: bool = False
+    block_size: int = 64
+    random_config: Optional[str] = None
+    weights_seed: int = 0
 
 
 def _int(text: str, what: str) -> int:
@@ -98,6 +105,12 @@ def parse_arguments(argv: List[str]) -> Arguments:
             args.stop_ids = (args.stop_ids or []) + [_int(value_of(word), "--stop-id")]
         elif word == "--ignore-eos":
             args.ignore_eos = True
+        elif word == "--block-size":
+            args.block_size = _int(value_of(word), "--block-size")
+        elif word == "--random":
+            args.random_config = value_of(word)
+        elif word == "--weights-seed":
+            args.weights_seed = _int(value_of(word), "--weights-seed")
         elif word == "--prompt-file":
             prompt_file = value_of(word)
         elif word.startswith("--"):
@@ -105,6 +118,8 @@ def parse_arguments(argv: List[str]) -> Arguments:
         else:
             positional.append(word)
         index += 1
+    if args.random_config is not None:
+        positional.insert(0, "")                  # no model folder: the configuration file stands for it
     needed = 2 if prompt_file else 3
     if len(positional) < needed:
         raise UsageError("expected a model path, max_new_tokens, and at least one prompt token")
@@ -145,10 +160,17 @@ def main(argv: Optional[List[str]] = None) -> int:
         if model.is_file():
             model = model.parent
         load_start = time.perf_counter()
-        block = 64
+        block = args.block_size
+        if block <= 0:
+            raise UsageError("--block-size must be positive")
         need = sum(-(-(len(p) + args.max_new_tokens) // block) * block for p in args.prompts)
         config = EngineConfig(max_tokens=args.max_tokens or need, dtype=args.dtype, block_size=block)
-        engine = Engine.from_folder(model, config)
+        if args.random_config is not None:
+            from .config import load_config
+            _, model_config = load_config(args.random_config)
+            engine = Engine.from_config(model_config, config, seed=args.weights_seed)
+        else:
+            engine = Engine.from_folder(model, config)
         load_ms = 1000.0 * (time.perf_counter() - load_start)
         output = engine.generate(args.prompts, args.max_new_tokens, params, stop_ids=args.stop_ids,
                                  ignore_eos=args.ignore_eos)

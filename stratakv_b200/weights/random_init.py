@@ -60,3 +60,24 @@ def write_random_model(folder, config, seed: int, dtype: torch.dtype = torch.bfl
     tensors = random_tensors(expected_tensors(spec), seed, std, dtype)
     write_safetensors(folder / "model.safetensors", tensors, metadata={"format": "pt"})
     return folder
+
+
+def main(argv=None) -> int:
+    """``python -m stratakv_b200.weights.random_init CONFIG.json OUT_DIR [--seed S] [--dtype bfloat16|float32]``:
+    write a model folder (config.json, model.safetensors) with random weights for a configuration."""
+    import argparse
+    from ..config import load_config
+    parser = argparse.ArgumentParser(prog="stratakv_b200.weights.random_init", description=main.__doc__)
+    parser.add_argument("config", help="a config.json (or a folder that holds one)")
+    parser.add_argument("out", help="folder to write")
+    parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "float16"])
+    args = parser.parse_args(argv)
+    _, config = load_config(args.config)
+    folder = write_random_model(args.out, config, args.seed, getattr(torch, args.dtype))
+    print(folder)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -134,6 +134,23 @@ def test_command_line(folders):
     assert subprocess.run([sys.executable, str(ROOT / "bin" / "stratakv_cli")], capture_output=True).returncode == 2
 
 
+def test_command_line_with_random_weights(tmp_path):
+    """--random CONFIG.json: no checkpoint; the same weights as the folder that the writer makes from the
+    same configuration and seed, so the plain implementation can check the tokens."""
+    import json
+    from stratakv_b200.weights import random_init
+    config_file = tmp_path / "config.json"
+    config_file.write_text(json.dumps(TINY["B"]))
+    assert random_init.main([str(config_file), str(tmp_path / "model"), "--seed", "9", "--dtype", "float32"]) == 0
+    config, weights = plain_llama.load_folder(tmp_path / "model")
+    prompt = random_tokens(TINY["B"]["vocab_size"], 5, seed=4)
+    command = [sys.executable, str(ROOT / "bin" / "stratakv_cli"), "--dtype", "float32", "--random", str(config_file),
+               "--weights-seed", "9", "--block-size", "16", "--ignore-eos", "6", *map(str, prompt)]
+    result = subprocess.run(command, capture_output=True, text=True, timeout=600)
+    assert result.returncode == 0, result.stderr
+    assert [int(t) for t in result.stdout.split()] == plain_llama.greedy(config, weights, prompt, 6)
+
+
 def test_python_entry_point(folders):
     from stratakv_b200.runner import run
     config, weights = plain_llama.load_folder(folders["A"])
