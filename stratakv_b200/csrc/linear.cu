@@ -355,7 +355,8 @@ static int launch_skinny_as(const void* a, const void* w, void* out, int M, int 
 // Warps per block.  Many row tiles (>= 4 per SM): 4 warps, compiled to fit 5 blocks on an SM so that
 // e.g. 704 tiles run as one wave.  Few row tiles: 8 warps (two blocks fit on an SM, so the next
 // kernel's weight loads overlap this one's end), or 16 when the inner size is so long that 8 warps
-// would need more than two rounds of loads each.  Never more warps than k steps.
+// would need more than two rounds of loads each and the tiles are no more than the SMs (a block of 16 warps
+// has an SM to itself; 256 tiles of 8 warps run as one wave, of 16 warps as two).  Never more warps than k steps.
 template <int TG, int U, int MAX_WARPS>
 static int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                          const NormArgs& norm, cudaStream_t stream) {
@@ -363,7 +364,11 @@ static int launch_skinny(const void* a, const void* w, void* out, int M, int N, 
     const int steps = (K + 31) / 32;
     const long long blocks = (long long)row_tiles * chunks;
     int warps = blocks >= 148 * 4 ? 4 : 8;
-    if (warps == 8 && MAX_WARPS >= 16 && steps > 8 * U * 2) warps = 16;
+    // A few more tiles than five blocks of 4 warps per SM hold (768 at hidden size 4096) would leave a second,
+    // nearly empty wave that doubles the time; blocks of 3 warps (96 registers a thread) fit 7 to an SM.  (Blocks
+    // of 2 warps or 1, of which 10 or 21 fit, measured slower than two waves.)
+    if (TG <= 2 && blocks > 148 * 5 && blocks <= 148 * 7) warps = 3;
+    if (warps == 8 && MAX_WARPS >= 16 && steps > 8 * U * 2 && blocks <= 148) warps = 16;   // (16 warps: one block per SM)
     if (warps > MAX_WARPS) warps = MAX_WARPS;
     while (warps > 1 && warps > steps) warps >>= 1;
     if (warps <= 4) return launch_skinny_as<TG, U, 4>(a, w, out, M, N, K, mode, act, warps, norm, stream);
