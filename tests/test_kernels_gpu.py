@@ -62,7 +62,8 @@ def pack_gate_up(w):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,N,K", [(1, 48, 64), (3, 331, 80), (8, 256, 2048), (9, 100, 264), (17, 96, 96),
                                    (33, 80, 176), (64, 512, 512), (70, 130, 520), (200, 64, 72),
-                                   (32, 2048, 5632), (64, 2560, 2048), (100, 1000, 1032), (128, 384, 4096)])
+                                   (32, 2048, 5632), (64, 2560, 2048), (100, 1000, 1032), (128, 384, 4096),
+                                   (5, 12288, 264)])          # 768 row tiles: blocks of 3 warps
 def test_linear_store_and_add(dtype, M, N, K):
     from stratakv_b200 import ops
     k = lib(dtype)
