@@ -3,10 +3,14 @@
 The reference's ``BlockPool`` is a LIFO list that hands out block 0 first and
 throws ``"OOM"`` when empty; its ``free_block`` checks nothing
 (``src/memory/block_pool.cpp:72-75, 193-207``).  Here an id can be held once
-only: freeing an id that is not held, or one outside the range, raises.
+only: freeing an id that is not held, or one outside the range, raises.  And the
+lowest free id is handed out first, always (a heap, not a stack): as requests
+come and go, a sequence's blocks then stay close together in the cache instead
+of being scattered over it in the order of earlier releases.
 """
 from __future__ import annotations
 
+import heapq
 from typing import Iterable, List
 
 
@@ -20,7 +24,7 @@ class IdAllocator:
             raise ValueError(f"number of {what}s must be positive")
         self.total = total
         self.what = what
-        self._free: List[int] = list(range(total - 1, -1, -1))   # id 0 is handed out first
+        self._free: List[int] = list(range(total))               # a heap: the lowest id is handed out first
         self._held = [False] * total
 
     @property
@@ -40,7 +44,7 @@ class IdAllocator:
             raise ValueError("count must be non-negative")
         if count > len(self._free):
             raise CacheFull(f"{count} {self.what}(s) wanted, {len(self._free)} of {self.total} free")
-        taken = [self._free.pop() for _ in range(count)]
+        taken = [heapq.heappop(self._free) for _ in range(count)]
         for ident in taken:
             self._held[ident] = True
         return taken
@@ -56,4 +60,4 @@ class IdAllocator:
             raise ValueError(f"a {self.what} id is freed twice in one call")
         for ident in idents:
             self._held[ident] = False
-            self._free.append(ident)
+            heapq.heappush(self._free, ident)

@@ -16,7 +16,7 @@ def test_allocator_hands_out_each_id_once():
         pool.take(3)
     assert pool.free_count == 2                                   # a refused request takes nothing
     pool.give_back([1])
-    assert pool.take(1) == [1]                                    # last freed, first reused
+    assert pool.take(1) == [1]                                    # the lowest free id first
     with pytest.raises(ValueError, match="not held"):
         pool.give_back([4])
     with pytest.raises(ValueError, match="outside"):
