@@ -529,7 +529,7 @@ def test_attention_prefill_at_the_edges_of_tiles_and_windows():
     (8, 2, 80, 64, [500, 16, 17], 0, 8, False),            # no rotation; more splits than work for some
     (2, 1, 32, 16, [9000, 300], 0, 4, True),               # a block table longer than the kernel keeps in shared memory
     (32, 4, 64, 64, [2048, 1500], 0, 4, True),             # few blocks: each stages its whole 512-key piece (four stages)
-XX
+    (8, 2, 128, 64, [700, 40], 0, 2, True),                # head size 128: swizzled rows of 256 bytes, three stages hold the piece
 ])
 def test_attention_decode_fused_equals_the_separate_kernels(heads, kv_heads, head_dim, block_size, lengths, window,
                                                             splits, rotate):
