@@ -159,3 +159,32 @@ def test_python_entry_point(folders):
                                      ignore_eos=True)
     assert sequences == [plain_llama.greedy(config, weights, prompt, 6)]
     assert timings.decode_tokens == 5 and engine.cache.all_free()
+
+
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_many_batches_twice_give_the_same_tokens(folders, name):
+    """Batches of many sizes (up to 24, so every projection kernel takes part), greedy and sampled, with
+    stop tokens and budgets that end requests early: nothing is left held afterwards, no kernel raises
+    a flag, and a second engine given the same requests returns the same tokens (no kernel's result
+    depends on timing)."""
+    import random
+    from stratakv_b200 import Engine, EngineConfig
+    from stratakv_b200.sampling import SamplingParams
+    vocab = TINY[name]["vocab_size"]
+
+    def run():
+        rng = random.Random(7)
+        engine = Engine.from_folder(folders[name], EngineConfig(max_tokens=4096, dtype="bfloat16", block_size=16),
+                                    verbose=False)
+        outputs = []
+        for round_ in range(8):
+            count = rng.choice([1, 3, 8, 9, 13, 17, 24])
+            prompts = [random_tokens(vocab, rng.randint(1, 90), seed=rng.randint(0, 10 ** 6)) for _ in range(count)]
+            budgets = [rng.randint(0, 30) for _ in range(count)]
+            params = SamplingParams() if round_ % 3 else SamplingParams(temperature=0.9, top_k=20, top_p=0.9, seed=round_)
+            stop = [rng.randrange(vocab) for _ in range(6)]
+            outputs.append(engine.generate(prompts, budgets, params, stop_ids=stop).sequences)
+            assert engine.cache.all_free()
+        return outputs
+
+    assert run() == run()
