@@ -138,13 +138,14 @@ def test_padding_and_company_change_nothing(folders, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_batches_that_do_not_fill_a_graph_bucket(folders, plain, dtype):
-    """Nine, then five, then eleven sequences decode together: the decode graph pads its batch up to
-    a bucket, and the padding rows (which read and write a spare cache block) must change nothing."""
+    """Nine, then five, eleven, twenty and forty sequences decode together: the decode graph pads its batch
+    up to a bucket, and the padding rows (which read and write a spare cache block) must change nothing.
+    The larger batches run their projections on the tensor-memory kernels for few tokens."""
     from stratakv_b200 import StepEntry
     name = "B"
-    engine = engine_for(folders[name], dtype, max_tokens=64 * 24)
+    engine = engine_for(folders[name], dtype, max_tokens=64 * 200)
     vocab = TINY[name]["vocab_size"]
-    for batch in (9, 5, 11):
+    for batch in (9, 5, 11, 20, 40):
         requests = []
         for i in range(batch):
             tokens = random_tokens(vocab, 3 + 5 * i + 6, seed=1000 + batch * 31 + i)
