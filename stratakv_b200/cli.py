@@ -13,7 +13,9 @@ come from ``config.json``, where the reference guesses them from tensor shapes.
 Added here: ``--seed S`` (reproducible draws; the reference documents the flag
 but does not have it), ``--dtype bfloat16|float32``, ``--max-tokens N`` (cache
 size), ``--stop-id ID`` (repeatable; default: the model's eos ids),
-``--ignore-eos``, ``--block-size N`` (cache block, default 64), ``--prompt-file FILE``
+``--ignore-eos``, ``--block-size N`` (cache block, default 64), ``--max-context N``
+(most positions a request may reach, in place of the model's ``max_position_embeddings``),
+``--prompt-file FILE``
 with one request per line, which are generated as a batch and printed one line
 each, and ``--random CONFIG.json``: no checkpoint, weights drawn from
 ``--weights-seed`` (default 0) for the configuration in that file; ``<model>`` is
@@ -29,7 +31,7 @@ from pathlib import Path
 from typing import List, Optional
 
 USAGE = ("Usage: stratakv_cli [--temp T] [--top-k K] [--top-p P] [--seed S] [--dtype bfloat16|float32]\n"
-         "                    [--max-tokens N] [--block-size N] [--stop-id ID]... [--ignore-eos]\n"
+         "                    [--max-tokens N] [--block-size N] [--max-context N] [--stop-id ID]... [--ignore-eos]\n"
          "                    [--prompt-file FILE] [--random CONFIG.json [--weights-seed S]]\n"
          "                    <model> <max_new_tokens> <prompt_id>...\n"
          "       options may also appear between max_new_tokens and the prompt tokens\n")
@@ -53,6 +55,7 @@ class Arguments:
     stop_ids: Optional[List[int]] = None
     ignore_eos: bool = False
     block_size: int = 64
+    max_context: int = 0
     random_config: Optional[str] = None
     weights_seed: int = 0
 
@@ -107,6 +110,10 @@ def parse_arguments(argv: List[str]) -> Arguments:
             args.ignore_eos = True
         elif word == "--block-size":
             args.block_size = _int(value_of(word), "--block-size")
+        elif word == "--max-context":
+            args.max_context = _int(value_of(word), "--max-context")
+            if args.max_context < 0:
+                raise UsageError("--max-context must be nonnegative")
         elif word == "--random":
             args.random_config = value_of(word)
         elif word == "--weights-seed":
@@ -164,7 +171,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         if block <= 0:
             raise UsageError("--block-size must be positive")
         need = sum(-(-(len(p) + args.max_new_tokens) // block) * block for p in args.prompts)
-        config = EngineConfig(max_tokens=args.max_tokens or need, dtype=args.dtype, block_size=block)
+        config = EngineConfig(max_tokens=args.max_tokens or need, dtype=args.dtype, block_size=block,
+                              max_context=args.max_context)
         if args.random_config is not None:
             from .config import load_config
             _, model_config = load_config(args.random_config)

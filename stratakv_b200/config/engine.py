@@ -33,13 +33,19 @@ class EngineConfig:
     """``max_tokens``: most tokens live requests hold at once, each request's
     count rounded up to a whole number of blocks.  ``block_size`` tokens per
     cache block.  ``max_batch``: most sequences in one step (0: as many as the
-    cache could hold at one block each)."""
+    cache could hold at one block each).  ``max_context``: most positions one
+    sequence may reach (prompt plus generated tokens); 0 takes the model's
+    ``max_position_embeddings``, a positive value replaces it (the rotary
+    encoding is defined at any position; what lies beyond the model's own limit
+    is the caller's decision).  The reference's only such limit is its cache
+    capacity (``src/generation/generator.cpp:628-632``)."""
     max_tokens: int
     dtype: torch.dtype = torch.bfloat16
     block_size: int = 64
     max_batch: int = 0
     device: str = "cuda:0"
     use_cuda_graphs: bool = True
+    max_context: int = 0
 
     def __post_init__(self):
         if self.max_tokens <= 0:
@@ -48,6 +54,8 @@ class EngineConfig:
             raise ConfigError("block_size must be a positive multiple of 16")
         if self.max_batch < 0:
             raise ConfigError("max_batch must be non-negative")
+        if self.max_context < 0:
+            raise ConfigError("max_context must be non-negative")
         object.__setattr__(self, "dtype", parse_dtype(self.dtype))
 
     @property

@@ -24,7 +24,10 @@
 #include "common.cuh"
 
 
-#if SKV_DTYPE == SKV_BF16
+// Two stages of 128 keys and values must fit one block's shared memory, which holds for head sizes up
+// to 192; above that this kernel is not built and the separate kernels (elementwise.cu,
+// attention_decode.cu) serve, as skv_has_attention_decode_fused() tells the caller.
+#if SKV_DTYPE == SKV_BF16 && SKV_HEAD_DIM <= 192
 
 namespace skv {
 
@@ -480,11 +483,16 @@ SKV_EXPORT int skv_attention_decode_fused(const float* qkv, const float* cos_sin
     return 0;
 }
 
+SKV_EXPORT int skv_has_attention_decode_fused() { return 1; }
+
 #else
 
 SKV_EXPORT int skv_attention_decode_fused(const float*, const float*, void*, void*, const int*, int, const int*, void*,
                                           int, int, int, int, int, float, int, int, int, cudaStream_t) {
-    return skv::fail("skv_attention_decode_fused", "only the bfloat16 build has this kernel");
+    return skv::fail("skv_attention_decode_fused",
+                     "this kernel exists in the bfloat16 build for head sizes up to 192 only");
 }
+
+SKV_EXPORT int skv_has_attention_decode_fused() { return 0; }
 
 #endif

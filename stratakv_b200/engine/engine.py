@@ -46,6 +46,8 @@ class Engine:
                  kernel_loader=None, verbose: bool = True):
         self.spec = spec
         self.config = config
+        # most positions a sequence may reach: the engine's setting, else the model's own limit, else none
+        self.max_context = config.max_context or spec.max_positions or 0
         if kernel_loader is None:
             self.device = _ops.require_cuda(config.device)
             kernel_loader = lambda dtype, head_dim: _ops.kernels_for(dtype, head_dim, verbose=verbose)
@@ -133,6 +135,7 @@ class Engine:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside this step's {len(e.tokens)} tokens")
             before = self.cache.length(e.slot)
+            self._check_context(e.slot, before + len(e.tokens))
             token_arrays.append(tokens)
             q_lens.append(len(e.tokens))
             ctx_before.append(before)
@@ -190,6 +193,11 @@ class Engine:
             cache=self.cache)
         return step, (view("want_rows") if want_rows else None), len(want_rows)
 
+    def _check_context(self, slot: int, length: int) -> None:
+        if self.max_context and length > self.max_context:
+            raise StepError(f"slot {slot}: the step would bring the sequence to {length} positions; "
+                            f"the limit is {self.max_context} (max_position_embeddings, or the engine's max_context)")
+
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step.  Returns float32 logits ``[wanted, vocab]`` on the device,
         in the order of the entries and of their ``want`` (``None`` when nothing
@@ -227,6 +235,9 @@ class Engine:
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside this step's 1 tokens")
                 rows.append(index)
         wanted = {slot: before + 1 for slot, before in zip(slots, ctx_before)}
+        if self.max_context and max(ctx_before) + 1 > self.max_context:
+            for slot, length in wanted.items():
+                self._check_context(slot, length)
         bucket = bucket_for(len(entries))
         graph = self._graphs.get(bucket)
         staged = graph is not None and graph.staged_for(slots, ctx_before)
@@ -317,15 +328,29 @@ class Engine:
         return output
 
     def check_flags(self) -> None:
-        """Raise if a kernel flagged bad input since the last check (reads one word from the device)."""
+        """Raise if a kernel flagged something since the last check (reads one word per flag from the
+        device).  The flags are cleared, so the engine can be used again afterwards."""
         flags = int(self.model.flags.item())
         for kernels in _ops._LOADED.values():
-            if kernels.error_flag is not None:
+            if getattr(kernels, "error_flag", None) is not None:
                 word = int(kernels.error_flag.item())
                 if word:
                     kernels.error_flag.zero_()
                     flags |= word
         if flags:
             self.model.flags.zero_()
-            raise StepError(f"device flags raised: {flags:#x} (1: token id outside the vocabulary, "
-                            "2: non-finite logits, 4: a wait inside a kernel timed out)")
+            raise StepError(f"device flags raised: {flags:#x} ({describe_flags(flags)})")
+
+
+FLAG_MEANINGS = {1: "a token id outside the vocabulary reached the embedding",
+                 2: "non-finite logits",
+                 4: "a wait inside a kernel timed out (its result is not valid)"}
+
+
+def describe_flags(word: int) -> str:
+    """The meaning of every bit set in a flag word that kernels raise."""
+    known = [text for bit, text in FLAG_MEANINGS.items() if word & bit]
+    unknown = word & ~sum(FLAG_MEANINGS)
+    if unknown:
+        known.append(f"unknown bits {unknown:#x}")
+    return "; ".join(known)

@@ -73,8 +73,9 @@ def plan_batches(needs: Sequence[int], free_blocks: int, free_slots: int) -> Lis
     return batches
 
 
-def validate_request(index: int, prompt: Sequence[int], max_new_tokens: int, vocab: int) -> None:
-    """src/generation/generator.cpp:619-626."""
+def validate_request(index: int, prompt: Sequence[int], max_new_tokens: int, vocab: int,
+                     max_context: int = 0) -> None:
+    """src/generation/generator.cpp:619-632: everything is checked before anything is touched."""
     if len(prompt) == 0:
         raise RequestError(f"request {index}: the prompt is empty")
     if max_new_tokens < 0:
@@ -82,6 +83,10 @@ def validate_request(index: int, prompt: Sequence[int], max_new_tokens: int, voc
     for token in prompt:
         if not isinstance(token, int) or isinstance(token, bool) or not (0 <= token < vocab):
             raise RequestError(f"request {index}: prompt token {token!r} is outside the vocabulary of {vocab}")
+    # the last chosen token is never fed, so a request reaches prompt + max_new_tokens - 1 positions in the cache
+    if max_context and max_new_tokens > 0 and len(prompt) + max_new_tokens - 1 > max_context:
+        raise RequestError(f"request {index}: a prompt of {len(prompt)} tokens plus {max_new_tokens} new ones "
+                           f"exceeds the context limit of {max_context}")
 
 
 def generate(engine, choose: Callable, prompts: Sequence[Sequence[int]], max_new_tokens,
@@ -91,8 +96,8 @@ def generate(engine, choose: Callable, prompts: Sequence[Sequence[int]], max_new
     """Serve ``prompts``.
 
     ``engine`` has ``open_sequence``, ``close_sequence``, ``step(entries)``, a
-    ``cache`` with ``block_size``, free block counts and free slots, and
-    ``spec.vocab_size``.  ``choose(logits, streams, counters)`` returns one token
+    ``cache`` with ``block_size``, free block counts and free slots,
+    ``spec.vocab_size`` and (optionally) ``max_context``.  ``choose(logits, streams, counters)`` returns one token
     id per row as a list of ints.  ``max_new_tokens`` is one number or one per
     request.  ``streams[i]`` names request ``i``'s random stream (default ``i``).
     """
@@ -103,8 +108,9 @@ def generate(engine, choose: Callable, prompts: Sequence[Sequence[int]], max_new
     streams = list(range(count)) if streams is None else list(streams)
     stop = frozenset(int(s) for s in stop_ids)
     vocab = engine.spec.vocab_size
+    max_context = getattr(engine, "max_context", 0)
     for index, prompt in enumerate(prompts):
-        validate_request(index, prompt, budgets[index], vocab)
+        validate_request(index, prompt, budgets[index], vocab, max_context)
     sequences = [list(p) for p in prompts]
     # src/generation/generator.cpp:627: nothing to do for these requests
     active = [i for i in range(count) if budgets[i] > 0 and sequences[i][-1] not in stop]

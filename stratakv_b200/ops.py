@@ -286,6 +286,9 @@ class Kernels:
             _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), n, num_heads, num_kv_heads, head_dim, block_size,
             ctypes.c_float(scale), window, splits, _stream()), "attention_decode")
 
+    def has_attention_decode_fused(self) -> bool:
+        return bool(self.lib.skv_has_attention_decode_fused())
+
     def attention_decode_fused(self, qkv, cos_sin, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
                                num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
                                splits: int = 1, write_kv: bool = True):

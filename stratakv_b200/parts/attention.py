@@ -100,7 +100,8 @@ class PagedAttention(Mixer):
         table = step.block_tables[step.cache.entry_group_index(cache_entry)]
         ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
         blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
-        fused = step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table")
+        fused = (step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table")
+                 and ops.has_attention_decode_fused())
         if fused:
             splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx, per_sm=2 if s.head_dim <= 64 else 1)
             fused = not wants_more_pieces(n, blocks_per_seq, step.max_ctx, splits)

@@ -5,7 +5,8 @@ first problem: ``"Missing weight: <name>"``, ``"Wrong shape/storage: <name>"``,
 and any tensor left over is ``"Unexpected weight: <name>"``
 (``src/generation/generator.cpp:265-289, 507-508``).  Here all problems of a
 checkpoint are collected into one ``WeightError`` that lists missing tensors,
-unexpected tensors and wrong shapes together.
+unexpected tensors, wrong shapes and tensors that hold a NaN or an infinity
+(``"Non-finite weight: <name>"``, ``src/generation/generator.cpp:274-285``) together.
 
 Tensors keep their stored dtype on the host: bfloat16 stays bfloat16, a tensor
 stored in 32 bits stays 32-bit, integer tables become int32.  Parts choose the
@@ -26,14 +27,16 @@ _INTEGER = (torch.int64, torch.int16, torch.int8, torch.uint8, torch.bool)
 
 
 class WeightError(ValueError):
-    """The checkpoint does not fit the model.  ``missing``, ``unexpected`` and
-    ``wrong_shape`` (name -> (expected, found)) hold the details."""
+    """The checkpoint does not fit the model.  ``missing``, ``unexpected``,
+    ``wrong_shape`` (name -> (expected, found)) and ``non_finite`` (names of
+    tensors with a NaN or an infinity in them) hold the details."""
 
-    def __init__(self, source, missing, unexpected, wrong_shape, wrong_dtype=()):
+    def __init__(self, source, missing, unexpected, wrong_shape, wrong_dtype=(), non_finite=()):
         self.missing = sorted(missing)
         self.unexpected = sorted(unexpected)
         self.wrong_shape = dict(wrong_shape)
         self.wrong_dtype = dict(wrong_dtype)
+        self.non_finite = sorted(non_finite)
         lines = [f"checkpoint {source} does not match the model:"]
         if self.missing:
             lines.append(f"  missing tensors ({len(self.missing)}): " + ", ".join(self.missing))
@@ -45,6 +48,8 @@ class WeightError(ValueError):
         if self.wrong_dtype:
             lines.append(f"  unusable dtypes ({len(self.wrong_dtype)}): " + ", ".join(
                 f"{n} is {d}" for n, d in sorted(self.wrong_dtype.items())))
+        if self.non_finite:
+            lines.append(f"  non-finite weights ({len(self.non_finite)}): " + ", ".join(self.non_finite))
         super().__init__("\n".join(lines))
 
 
@@ -86,6 +91,7 @@ def check_and_select(source, tensors: Mapping[str, torch.Tensor],
     wrong_shape = {n: (tuple(expected[n]), tuple(tensors[n].shape)) for n in expected
                    if n in tensors and tuple(tensors[n].shape) != tuple(expected[n])}
     wrong_dtype = {}
+    non_finite = []
     selected = {}
     for name in expected:
         if name not in tensors or name in wrong_shape:
@@ -96,9 +102,12 @@ def check_and_select(source, tensors: Mapping[str, torch.Tensor],
         elif tensor.dtype == torch.float64:
             wrong_dtype[name] = "F64"
             continue
+        elif not bool(torch.isfinite(tensor).all()):
+            non_finite.append(name)
+            continue
         selected[name] = tensor
-    if missing or unexpected or wrong_shape or wrong_dtype:
-        raise WeightError(source, missing, unexpected, wrong_shape, wrong_dtype)
+    if missing or unexpected or wrong_shape or wrong_dtype or non_finite:
+        raise WeightError(source, missing, unexpected, wrong_shape, wrong_dtype, non_finite)
     return selected
 
 

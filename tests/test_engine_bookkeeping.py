@@ -16,12 +16,14 @@ from stratakv_b200.engine.model import expected_tensors
 from stratakv_b200.weights import load_checkpoint
 
 
-def cpu_engine(folder, max_tokens=512, block_size=16):
+def cpu_engine(folder, max_tokens=512, block_size=16, max_context=None):
     arch, config = load_config(folder)
     spec = arch.build_spec(config)
     tensors = load_checkpoint(folder, {n: r.shape for n, r in expected_tensors(spec).items()}, spec.ignorable)
     return Engine(spec, tensors, EngineConfig(max_tokens=max_tokens, dtype="float32", device="cpu",
-                                              block_size=block_size), kernel_loader=double_loader())
+                                              block_size=block_size,
+                                              max_context=max_tokens if max_context is None else max_context),
+                  kernel_loader=double_loader())
 
 
 @pytest.mark.parametrize("name", ["A", "B"])
@@ -49,7 +51,7 @@ def test_cuttings_agree_with_the_plain_model(tmp_path, name):
 
 def test_step_checks(tmp_path):
     folder = make_folder(tmp_path / "A", TINY["A"], seed=4)
-    engine = cpu_engine(folder, max_tokens=64)
+    engine = cpu_engine(folder, max_tokens=64, max_context=1000)
     slot = engine.open_sequence()
     with pytest.raises(StepError, match="outside the vocabulary"):
         engine.step([StepEntry(slot, [1, 256], [0])])
@@ -121,3 +123,56 @@ def test_schedule_may_repeat_a_layer_and_share_a_cache(tmp_path):
         got = engine.step([StepEntry(slot, [tokens[position]], [0])])
         np.testing.assert_allclose(got.numpy()[0], ref[position].numpy(), rtol=1e-4, atol=2e-5)
     engine.close_sequence(slot)
+
+
+def test_the_context_limit_holds_in_every_step(tmp_path):
+    """A sequence may reach max_position_embeddings positions (64 for configuration A) and no more,
+    whether the step brings many tokens or one; an engine-level max_context replaces the model's limit."""
+    folder = make_folder(tmp_path / "A", TINY["A"], seed=4)
+    engine = cpu_engine(folder, max_tokens=256, max_context=0)
+    assert engine.max_context == 64
+    slot = engine.open_sequence()
+    with pytest.raises(StepError, match="65 positions; the limit is 64"):
+        engine.step([StepEntry(slot, [1] * 65, [])])
+    assert engine.cache.length(slot) == 0 and engine.cache.free_blocks() == [16]    # nothing was taken
+    engine.step([StepEntry(slot, [1] * 63, [])])
+    engine.step([StepEntry(slot, [2], [0])])
+    with pytest.raises(StepError, match="slot 0: the step would bring the sequence to 65 positions"):
+        engine.step([StepEntry(slot, [3], [0])])
+    assert engine.cache.length(slot) == 64
+    engine.close_sequence(slot)
+    wider = cpu_engine(folder, max_tokens=256, max_context=100)
+    slot = wider.open_sequence()
+    wider.step([StepEntry(slot, [1] * 100, [])])
+    with pytest.raises(StepError, match="the limit is 100"):
+        wider.step([StepEntry(slot, [1], [])])
+
+
+def test_flag_words_are_decoded_and_cleared(tmp_path):
+    """Kernels report trouble by raising bits in a device word; nothing here makes a kernel wait or
+    fail: the words are written by the test, and the host's reading of them is what is checked."""
+    from stratakv_b200 import ops
+    folder = make_folder(tmp_path / "A", TINY["A"], seed=4)
+    engine = cpu_engine(folder)
+    engine.check_flags()                                         # nothing raised: no error
+    engine.model.flags[0] = 4
+    with pytest.raises(StepError, match=r"0x4 \(a wait inside a kernel timed out"):
+        engine.check_flags()
+    engine.check_flags()                                         # cleared by the report
+    engine.model.flags[0] = 3
+    with pytest.raises(StepError, match=r"0x3 \(a token id outside the vocabulary.*; non-finite logits\)"):
+        engine.check_flags()
+
+    class LoadedLibrary:                                         # a kernel library's own flag word
+        error_flag = torch.tensor([4], dtype=torch.int32)
+    ops._LOADED[("forged", 0)] = LoadedLibrary()
+    try:
+        engine.model.flags[0] = 2
+        with pytest.raises(StepError, match=r"0x6 \(non-finite logits; a wait inside a kernel timed out"):
+            engine.check_flags()
+        assert int(LoadedLibrary.error_flag) == 0 and int(engine.model.flags) == 0
+        engine.model.flags[0] = 8
+        with pytest.raises(StepError, match=r"unknown bits 0x8"):
+            engine.check_flags()
+    finally:
+        del ops._LOADED[("forged", 0)]

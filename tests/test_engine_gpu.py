@@ -34,7 +34,8 @@ def plain(folders):
 
 def engine_for(folder, dtype, max_tokens=2048, block_size=64):
     from stratakv_b200 import Engine, EngineConfig
-    return Engine.from_folder(folder, EngineConfig(max_tokens=max_tokens, dtype=dtype, block_size=block_size),
+    return Engine.from_folder(folder, EngineConfig(max_tokens=max_tokens, dtype=dtype, block_size=block_size,
+                                                      max_context=max_tokens),
                               verbose=False)
 
 

@@ -22,7 +22,7 @@ def folders(tmp_path_factory):
 
 def engine_for(folder, dtype, max_tokens=4096):
     from stratakv_b200 import Engine, EngineConfig
-    return Engine.from_folder(folder, EngineConfig(max_tokens=max_tokens, dtype=dtype), verbose=False)
+    return Engine.from_folder(folder, EngineConfig(max_tokens=max_tokens, dtype=dtype, max_context=max_tokens), verbose=False)
 
 
 @pytest.mark.parametrize("name", ["A", "B"])
@@ -174,7 +174,7 @@ def test_many_batches_twice_give_the_same_tokens(folders, name):
 
     def run():
         rng = random.Random(7)
-        engine = Engine.from_folder(folders[name], EngineConfig(max_tokens=4096, dtype="bfloat16", block_size=16),
+        engine = Engine.from_folder(folders[name], EngineConfig(max_tokens=4096, dtype="bfloat16", block_size=16, max_context=4096),
                                     verbose=False)
         outputs = []
         for round_ in range(8):

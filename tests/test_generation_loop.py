@@ -125,3 +125,16 @@ def test_streams_and_counters_follow_the_request():
         return choose(logits, streams, counters)
     generate(engine, spy, [[1], [2], [3]], [3, 1, 2], streams=[7, 8, 9])
     assert seen == [([7, 8, 9], [0, 0, 0]), ([7, 9], [1, 1]), ([7], [2])]
+
+
+def test_a_request_beyond_the_context_limit_is_refused_before_anything_runs():
+    """src/generation/generator.cpp:619-632 refuses what cannot fit before it touches anything; the
+    limit here is the engine's ``max_context`` (the model's max_position_embeddings unless overridden)."""
+    engine = ScriptedEngine()
+    engine.max_context = 12
+    # a prompt of 8 and 5 new tokens holds 12 positions (the last chosen token is never fed): allowed
+    assert len(generate(engine, choose, [[1] * 8], 5).sequences[0]) == 13
+    with pytest.raises(RequestError, match=r"request 1: a prompt of 8 tokens plus 6 new ones exceeds the context limit of 12"):
+        generate(engine, choose, [[1, 2], [1] * 8], [3, 6])
+    assert engine.steps[-1][0][1] != [1, 2] and engine.cache.all_free()      # the first request did not run either
+    assert generate(engine, choose, [[1] * 40], 0).sequences == [[1] * 40]   # nothing to run, nothing to refuse

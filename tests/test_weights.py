@@ -149,3 +149,68 @@ def test_integer_tables_become_int32(tmp_path):
     from stratakv_b200.weights import check_and_select
     picked = check_and_select("x", {"table": torch.arange(4, dtype=torch.int64)}, {"table": (4,)})
     assert picked["table"].dtype == torch.int32
+
+
+@pytest.mark.parametrize("dtype,bad", [(torch.float32, float("nan")), (torch.bfloat16, float("inf")),
+                                       (torch.float32, float("-inf"))])
+def test_a_non_finite_weight_is_refused_by_name(tmp_path, dtype, bad):
+    """src/generation/generator.cpp:274-285: "Non-finite weight: <name>"; here it joins the one error."""
+    folder = make_folder(tmp_path / "m", TINY_A, seed=3, dtype=dtype)
+    tensors = {name: tensor.clone() for name, tensor in read_checkpoint(folder).items()}
+    tensors["model.layers.1.mlp.down_proj.weight"][5, 7] = bad
+    tensors["model.norm.weight"][0] = bad
+    del tensors["lm_head.weight"]
+    write_safetensors(folder / "model.safetensors", tensors)
+    spec, shapes = expected_shapes(TINY_A)
+    with pytest.raises(WeightError) as info:
+        load_checkpoint(folder, shapes, spec.ignorable)
+    assert info.value.non_finite == ["model.layers.1.mlp.down_proj.weight", "model.norm.weight"]
+    assert info.value.missing == ["lm_head.weight"]
+    assert "non-finite weights (2): model.layers.1.mlp.down_proj.weight, model.norm.weight" in str(info.value)
+
+
+def shard(folder, tensors, parts):
+    """Rewrite a folder's checkpoint as ``parts`` shards with an index, the way large checkpoints ship."""
+    names = sorted(tensors)
+    weight_map = {}
+    for part in range(parts):
+        file_name = f"model-{part + 1:05d}-of-{parts:05d}.safetensors"
+        mine = {name: tensors[name] for name in names[part::parts]}
+        write_safetensors(folder / file_name, mine)
+        weight_map.update({name: file_name for name in mine})
+    (folder / "model.safetensors").unlink()
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    return weight_map
+
+
+def test_a_sharded_folder_round_trips(tmp_path):
+    folder = make_folder(tmp_path / "m", TINY_B, seed=4, dtype=torch.bfloat16)
+    whole = {name: tensor.clone() for name, tensor in read_checkpoint(folder).items()}
+    shard(folder, whole, 3)
+    spec, shapes = expected_shapes(TINY_B)
+    loaded = load_checkpoint(folder, shapes, spec.ignorable)
+    assert set(loaded) == set(shapes)
+    assert all(torch.equal(loaded[name], whole[name]) for name in loaded)
+
+
+def test_a_tensor_in_two_shards_is_refused(tmp_path):
+    folder = make_folder(tmp_path / "m", TINY_A, seed=4)
+    whole = {name: tensor.clone() for name, tensor in read_checkpoint(folder).items()}
+    weight_map = shard(folder, whole, 2)
+    first, second = sorted(set(weight_map.values()))
+    copied = next(name for name, file_name in weight_map.items() if file_name == first)
+    again = {name: whole[name] for name, file_name in weight_map.items() if file_name == second}
+    again[copied] = whole[copied]
+    write_safetensors(folder / second, again)
+    with pytest.raises(SafetensorsError, match="more than one shard"):
+        read_checkpoint(folder)
+
+
+def test_a_missing_shard_is_named(tmp_path):
+    folder = make_folder(tmp_path / "m", TINY_A, seed=4)
+    whole = {name: tensor.clone() for name, tensor in read_checkpoint(folder).items()}
+    weight_map = shard(folder, whole, 2)
+    gone = sorted(set(weight_map.values()))[1]
+    (folder / gone).unlink()
+    with pytest.raises(SafetensorsError, match=gone):
+        read_checkpoint(folder)
