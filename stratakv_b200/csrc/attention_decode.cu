@@ -19,6 +19,8 @@
 // then head-dim element g*head_dim/8 + j, undone when the output is written.
 #include "common.cuh"
 
+#include <mutex>
+
 #if SKV_DTYPE == SKV_BF16
 
 namespace skv {
@@ -337,8 +339,12 @@ SKV_EXPORT int skv_attention_decode_no_alloc(const void* q, const void* k_cache,
     // In host code the array's name is a stand-in, not a device address.  The address the kernel
     // needs is asked for once per device, with that device current (the first call on a device
     // does it, which is why that call should come before any stream capture).
+    // The per-device records below are read and written under one host lock, so that two host threads
+    // making their first call at once do not race on them.
+    static std::mutex setup_lock;
     static float* scratch_of_device[NO_ALLOC_MAX_DEVICES] = {nullptr};
     static bool attribute_set[NO_ALLOC_MAX_DEVICES] = {false};
+    std::lock_guard<std::mutex> setup_guard(setup_lock);
     int device = -1;
     cudaError_t status = cudaGetDevice(&device);
     if (status != cudaSuccess) return fail("skv_attention_decode_no_alloc", cudaGetErrorString(status));

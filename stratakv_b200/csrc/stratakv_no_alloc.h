@@ -22,7 +22,9 @@
  *   - All calls share the one array and it keeps what the last call left there.  The kernels
  *     write every slot they later read, so stale contents do no harm, but two calls that
  *     overlap on the GPU (different streams, or graphs replayed side by side) race on it.
- *     Serialise them.
+ *     Serialise them.  On the host side the entry point may be called from several threads:
+ *     its per-device set-up is done under a lock.  That lock orders host threads only; it
+ *     does nothing about two calls whose kernels overlap on the GPU.
  *
  * Arguments are those of skv_attention_decode without the two scratch pointers: bfloat16
  * q [n_seqs, num_heads * head_dim], the cache of one layer [blocks][kv_heads][block_size]

@@ -20,15 +20,17 @@ import numpy as np
 import torch
 
 
-def load_folder(model_dir):
-    """``(config dict, {name: float32 tensor})`` of a model folder."""
+def load_folder(model_dir, device="cpu"):
+    """``(config dict, {name: float32 tensor})`` of a model folder.  ``device`` is where the tensors
+    go: the arithmetic below runs wherever its weights are (large test models use a GPU for speed,
+    in the same float32 and double steps)."""
     from safetensors import safe_open
     model_dir = Path(model_dir)
     config = json.loads((model_dir / "config.json").read_text())
     weights = {}
     with safe_open(str(model_dir / "model.safetensors"), framework="pt") as handle:
         for name in handle.keys():
-            weights[name] = handle.get_tensor(name).to(torch.float32)
+            weights[name] = handle.get_tensor(name).to(device=device, dtype=torch.float32)
     return config, weights
 
 
@@ -37,7 +39,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     float, ``1/sqrt(mean + eps)`` in float, then ``x * inv * weight``."""
     mean_square = (x.double() ** 2).sum(dim=-1, keepdim=True) / x.shape[-1]
     mean_square = mean_square.float()
-    inverse_rms = 1.0 / torch.sqrt(mean_square + torch.tensor(eps, dtype=torch.float32))
+    inverse_rms = 1.0 / torch.sqrt(mean_square + torch.tensor(eps, dtype=torch.float32, device=x.device))
     return x * inverse_rms * weight
 
 
@@ -47,8 +49,9 @@ def rope_angles(head_dim: int, theta: float, positions: torch.Tensor):
     half = head_dim // 2
     exponent = -2.0 * np.arange(half, dtype=np.float64) / float(head_dim)
     inv_freq = np.power(np.float64(theta), exponent).astype(np.float32).astype(np.float64)
-    angle = positions.double().numpy()[:, None] * inv_freq[None, :]
-    return (torch.from_numpy(np.cos(angle)).float(), torch.from_numpy(np.sin(angle)).float())
+    angle = positions.double().cpu().numpy()[:, None] * inv_freq[None, :]
+    return (torch.from_numpy(np.cos(angle)).float().to(positions.device),
+            torch.from_numpy(np.sin(angle)).float().to(positions.device))
 
 
 def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -71,7 +74,7 @@ def attention(q, k, v, scale: float, window: int = 0):
     for h in range(heads):
         g = h // group
         scores = (q[:, h, :] @ k[:, g, :].T) * scale                  # [T, T]
-        index = torch.arange(tokens)
+        index = torch.arange(tokens, device=q.device)
         mask = index[None, :] > index[:, None]
         if window > 0:
             mask = mask | (index[None, :] <= index[:, None] - window)
@@ -123,9 +126,10 @@ def logits_of(config, weights, tokens) -> torch.Tensor:
     """Logits ``[len(tokens), vocab]`` at every position of one whole sequence
     (src/generation/generator.cpp:520-529 embedding, :554-568 layers, :773-774
     final norm and head)."""
-    ids = torch.tensor(list(tokens), dtype=torch.long)
+    device = weights["model.embed_tokens.weight"].device
+    ids = torch.tensor(list(tokens), dtype=torch.long, device=device)
     x = weights["model.embed_tokens.weight"][ids]
-    positions = torch.arange(len(ids))
+    positions = torch.arange(len(ids), device=device)
     for layer in range(config["num_hidden_layers"]):
         x = decoder_layer(x, weights, layer, config, positions)
     x = rmsnorm(x, weights["model.norm.weight"], config["rms_norm_eps"])

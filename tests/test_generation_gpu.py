@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_llama
-from helpers import ROOT, TINY, make_folder, random_tokens, tolerance
+from helpers import ROOT, TINY, make_folder, random_tokens, stored_dtype, tolerance
 
 pytestmark = pytest.mark.gpu
 
@@ -17,7 +17,12 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("gen_models")
-    return {name: make_folder(root / name, raw, seed=31 + i) for i, (name, raw) in enumerate(TINY.items())}
+    made = {name: make_folder(root / name, raw, seed=31 + i) for i, (name, raw) in enumerate(TINY.items())}
+    # the same weights stored in bfloat16, for runs that compute in bfloat16 (the plain model then sees the same values)
+    made.update({(name, "bfloat16"): make_folder(root / (name + "_bf16"), raw, seed=31 + i, dtype="bfloat16")
+                 for i, (name, raw) in enumerate(TINY.items())})
+    made.update({(name, "float32"): made[name] for name in TINY})
+    return made
 
 
 def engine_for(folder, dtype, max_tokens=4096):
@@ -42,16 +47,16 @@ def test_greedy_float32_equals_the_plain_model(folders, name):
 def test_greedy_bfloat16_picks_a_top_token(folders, name):
     """In bfloat16 near-ties may fall the other way: every chosen token must score within
     the bfloat16 tolerance of the plain model's best, given the same tokens before it."""
-    config, weights = plain_llama.load_folder(folders[name])
-    engine = engine_for(folders[name], "bfloat16")
+    config, weights = plain_llama.load_folder(folders[name, "bfloat16"])
+    engine = engine_for(folders[name, "bfloat16"], "bfloat16")
     prompts = [random_tokens(TINY[name]["vocab_size"], n, seed=n) for n in (4, 19)]
     out = engine.generate(prompts, 10, ignore_eos=True)
-    _, atol = tolerance("bfloat16")
     for prompt, sequence in zip(prompts, out.sequences):
         assert sequence[:len(prompt)] == prompt and len(sequence) == len(prompt) + 10
         logits = plain_llama.logits_of(config, weights, sequence[:-1]).numpy()
         for position in range(len(prompt) - 1, len(sequence) - 1):
             row = logits[position]
+            _, atol = tolerance("bfloat16", row)
             assert row[sequence[position + 1]] >= row.max() - 2 * atol
 
 
@@ -105,11 +110,11 @@ def test_sampling_batched_equals_solo_and_is_seeded(folders, dtype):
 def test_long_decoding(folders, dtype):
     """Four hundred tokens one by one (many cache blocks), checked against whole-sequence logits."""
     from stratakv_b200 import StepEntry
-    config, weights = plain_llama.load_folder(folders["C"])
-    engine = engine_for(folders["C"], dtype)
+    config, weights = plain_llama.load_folder(folders["C", dtype])
+    engine = engine_for(folders["C", dtype], dtype)
     tokens = random_tokens(331, 400, seed=3)
     ref = plain_llama.logits_of(config, weights, tokens).numpy()
-    rtol, atol = tolerance(dtype)
+    rtol, atol = tolerance(dtype, ref)
     slot = engine.open_sequence()
     for position, token in enumerate(tokens):
         got = engine.step([StepEntry(slot, [token], [0])])

@@ -110,6 +110,69 @@ def test_linear_gated(dtype, M, F, K):
         close(out, ref, dtype)
 
 
+def _products(a, w, chunk=512):
+    """``a . w^T`` and ``|a| . |w|^T`` in double on the GPU, a few hundred rows at a time."""
+    wd = w.double()
+    wa = wd.abs()
+    ref = torch.cat([a[i:i + chunk].double() @ wd.T for i in range(0, a.shape[0], chunk)])
+    bound = torch.cat([a[i:i + chunk].double().abs() @ wa.T for i in range(0, a.shape[0], chunk)])
+    return ref, bound
+
+
+# Shapes of the projections of real models (hidden 2048, feed-forward 5632, vocabulary 32000, and an odd
+# vocabulary of 32001 whose rows are no multiple of 16 bytes, so that threads store instead of the copy
+# engine).  They make the persistent tensor-memory kernel walk several tiles per block, wrap its ring of
+# stages many times (K / 64 steps over four stages), use both tile widths and add into many row tiles.
+@pytest.mark.parametrize("M,N,K,modes", [
+    (129, 2048, 2048, "store_f32 store add"),        # 128-wide tiles, one tile per block, a tail of one row
+    (300, 2560, 2048, "store_f32 store add"),        # the q|k|v projection of a short prompt
+    (2048, 2560, 2048, "store_f32 add"),             # 256-wide tiles: 160 tiles on 148 blocks
+    (2048, 2048, 5632, "store add"),                 # the down projection: 88 steps of K
+    (4096, 2048, 5632, "add"),                       # 256 tiles, residual sum through the copy engine
+    (2048, 11264, 2048, "gated"),                    # gate and up: 704 tiles, almost five per block
+    (4096, 32000, 2048, "store_f32"),                # the output head over every position: 27 tiles per block
+    (300, 32001, 2048, "store_f32 store add"),       # rows of an odd width: stored by the threads
+    (2048, 32001, 2048, "store_f32"),
+    (1000, 4112, 1032, "store_f32 store add gated"),  # tails in M, N and K at once
+])
+def test_linear_tiled_tensor_memory_kernel_at_model_sizes(M, N, K, modes):
+    """tests/gemv_smoke.cu:329-357 takes the reference's kernels to the model's shapes with a bound from
+    the sum of |a||w| (:259-272); the same here for steps of more than 128 tokens."""
+    from stratakv_b200 import ops
+    dtype = torch.bfloat16
+    k = lib(dtype)
+    a = torch.randn(M, K, device="cuda").to(dtype)
+    w = (torch.randn(N, K, device="cuda") / math.sqrt(K)).to(dtype)
+    ref, bound = _products(a, w)
+    allowed = 2e-6 * (1 + bound)
+    for mode in modes.split():
+        if mode == "store_f32":
+            out = torch.full((M, N), float("nan"), device="cuda")
+            k.linear(a, w, out, ops.MODE_STORE_F32)
+            assert ((out.double() - ref).abs() <= allowed).all(), mode
+        elif mode == "store":
+            out = torch.full((M, N), float("nan"), device="cuda").to(dtype)
+            k.linear(a, w, out, ops.MODE_STORE)
+            assert ((out.double() - ref).abs() <= allowed + 2.0 ** -8 * ref.abs()).all(), mode
+        elif mode == "add":
+            base = torch.randn(M, N, device="cuda")
+            acc = base.clone()
+            k.linear(a, w, acc, ops.MODE_ADD_F32)
+            k.linear(a, w, acc, ops.MODE_ADD_F32)       # adds again
+            assert ((acc.double() - (base.double() + 2 * ref)).abs() <= 2 * allowed + 1e-6 * base.abs()).all(), mode
+        else:
+            F = N // 2
+            out = torch.full((M, F), float("nan"), device="cuda").to(dtype)
+            k.linear(a, pack_gate_up(w), out, ops.MODE_GATED, "silu")
+            gate, up = ref[:, :F], ref[:, F:]
+            want = gate * torch.sigmoid(gate) * up
+            slack = (1.1 * allowed[:, :F] * up.abs() + (gate * torch.sigmoid(gate)).abs() * allowed[:, F:]
+                     + 2.0 ** -8 * want.abs() + 1e-9)
+            assert ((out.double() - want).abs() <= slack).all(), mode
+        torch.cuda.synchronize()
+        assert int(k.error_flag.item()) == 0
+
+
 class _Norm:
     """Stands for a norm part: all the kernels want of it is its weight and eps."""
     def __init__(self, gamma, eps):
@@ -597,3 +660,126 @@ def test_attention_prefill_tcgen05(heads, kv_heads, head_dim, block_size, length
     assert int(k.error_flag.item()) == 0
     ref = attention_reference(setup, dtype, heads, kv_heads, scale, window).view(n, -1)
     close(out, ref, dtype)
+
+
+def _rotate_plain(x, theta, positions):
+    """Split-half rotation of ``x`` [n, heads, d] in float with angles taken in double
+    (src/layers/attention.cpp:63-69, 96-135)."""
+    half = x.shape[-1] // 2
+    inv = torch.tensor([theta ** (-2.0 * i / x.shape[-1]) for i in range(half)], dtype=torch.float64).float().double()
+    angle = positions.double()[:, None] * inv[None, :]
+    cos, sin = torch.cos(angle).float()[:, None], torch.sin(angle).float()[:, None]
+    return torch.cat([x[..., :half] * cos - x[..., half:] * sin, x[..., :half] * sin + x[..., half:] * cos], -1)
+
+
+def _fused_decode_case(dtype, lengths, heads, kv_heads, head_dim, block_size, seed, theta=5000.0):
+    """A paged cache with ``lengths[s] - 1`` keys per sequence and one new token each as a float q|k|v row;
+    returns the kernel's inputs and a ``setup`` for ``attention_reference`` in which the rotated new key and
+    the new value stand at the last position and the rotated queries are the queries."""
+    from stratakv_b200.parts.position import rope_table
+    n = len(lengths)
+    setup = paged_setup(dtype, lengths, [1] * n, heads, kv_heads, head_dim, block_size, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    qkv = torch.randn(n, (heads + 2 * kv_heads) * head_dim, generator=g)
+    positions = torch.tensor([l - 1 for l in lengths])
+    q = _rotate_plain(qkv[:, :heads * head_dim].view(n, heads, head_dim), theta, positions)
+    new_k = _rotate_plain(qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].view(n, kv_heads, head_dim), theta, positions)
+    new_v = qkv[:, (heads + kv_heads) * head_dim:].view(n, kv_heads, head_dim)
+    setup["q"] = q.to(dtype).cuda()
+    for s, length in enumerate(lengths):
+        setup["keys"][s][length - 1] = new_k[s]
+        setup["values"][s][length - 1] = new_v[s]
+    table = torch.from_numpy(rope_table(head_dim, theta, max(lengths) + 8)).cuda()
+    return setup, qkv.cuda(), table, q
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size,lengths,window,splits", [
+    (4, 2, 16, 16, [5, 40, 17, 1], 0, 1),
+    (32, 4, 64, 64, [700, 129, 2048, 64, 65], 0, 8),       # the TinyLlama head layout
+    (32, 4, 64, 64, [2048] * 8, 0, 4),                     # the benchmark's step: whole 512-key pieces staged
+    (32, 32, 128, 64, [300, 1000], 0, 2),                  # one query head per KV head, head size 128
+    (32, 8, 128, 64, [2048, 77], 0, 8),
+    (20, 1, 32, 16, [90, 45], 0, 4),                       # more than 16 query heads on one KV head
+    (4, 2, 32, 16, [90, 45, 7], 20, 2),                    # a window
+    (2, 1, 192, 32, [150], 0, 2),                          # the largest head size this kernel is built for
+])
+def test_attention_decode_fused_against_plain_attention(heads, kv_heads, head_dim, block_size, lengths, window, splits):
+    """The fused kernel against attention written out in double (not against the other kernels)."""
+    dtype = torch.bfloat16
+    k = lib(dtype, head_dim)
+    assert k.has_attention_decode_fused()
+    setup, qkv, table, _ = _fused_decode_case(dtype, lengths, heads, kv_heads, head_dim, block_size, seed=heads + head_dim)
+    n = len(lengths)
+    scale = 0.5 / math.sqrt(head_dim)
+    out = torch.full((n, heads * head_dim), float("nan"), device="cuda").to(dtype)
+    k.attention_decode_fused(qkv, table, setup["k_cache"], setup["v_cache"], setup["table"],
+                             torch.tensor(lengths, dtype=torch.int32, device="cuda"), out, heads, kv_heads, head_dim,
+                             block_size, scale, window, splits, True)
+    ref = attention_reference(setup, dtype, heads, kv_heads, scale, window).view(n, -1)
+    close(out, ref, dtype)
+
+
+@pytest.mark.parametrize("head_dim,splits", [(64, 1), (64, 4), (64, 8), (128, 2)])
+def test_attention_decode_fused_finds_one_far_key_and_ignores_what_lies_beyond(head_dim, splits):
+    """One key among two thousand dominates, wherever it lies (the first key, a piece's edge, the key just
+    written); rows of the last block beyond the length hold huge values that must not leak in."""
+    dtype, heads, kv_heads, block_size = torch.bfloat16, 8, 2, 64
+    k = lib(dtype, head_dim)
+    for far, length in ((0, 2000), (499, 2000), (500, 2000), (1023, 2000), (1998, 2000), (64, 66), (127, 129)):
+        setup, qkv, table, q = _fused_decode_case(dtype, [length], heads, kv_heads, head_dim, block_size, seed=far)
+        key = 8.0 * q[0, 5] / q[0, 5].norm()                    # head 5 uses kv head 1; q is already rotated
+        block = int(setup["table"][0, far // block_size])
+        setup["k_cache"][block, 1, far % block_size] = key.to(dtype)
+        setup["keys"][0][far, 1] = key
+        last = int(setup["table"][0, (length - 1) // block_size])
+        setup["k_cache"][last, :, length % block_size:] = 100.0   # stale rows past the end
+        setup["v_cache"][last, :, length % block_size:] = 1e4
+        out = torch.zeros(1, heads * head_dim, device="cuda").to(dtype)
+        k.attention_decode_fused(qkv, table, setup["k_cache"], setup["v_cache"], setup["table"],
+                                 torch.tensor([length], dtype=torch.int32, device="cuda"), out, heads, kv_heads,
+                                 head_dim, block_size, 4.0, 0, splits, True)
+        ref = attention_reference(setup, dtype, heads, kv_heads, 4.0).view(1, -1)
+        close(out, ref, dtype)
+        want = setup["values"][0][far, 1].to(dtype).float()
+        torch.testing.assert_close(out[0, 5 * head_dim:6 * head_dim].float().cpu(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_attention_prefill_tcgen05_at_the_edges_of_tiles_and_windows(head_dim):
+    """Single keys made to dominate where masks and tiles meet in the tensor-memory kernel: the causal edge
+    (the query's own key), the last key of a 64-key tile and the first of the next, the edges of the
+    128-query tiles, the first key inside a window and the last one outside it (which must not be seen),
+    with part of the context cached by earlier steps."""
+    dtype, heads, kv_heads, block_size = torch.bfloat16, 2, 1, 16
+    k = lib(dtype, head_dim)
+    length = 330
+    cases = [(0, 200, 200, True), (0, 200, 63, True), (0, 200, 64, True), (0, 127, 127, True), (0, 128, 127, True),
+             (0, 128, 128, True), (0, 329, 0, True), (0, 255, 191, True), (0, 256, 192, True),
+             (100, 200, 101, True), (100, 200, 100, False), (100, 329, 230, True), (100, 329, 229, False),
+             (100, 128, 29, True), (100, 128, 28, False), (70, 300, 0, False)]
+    for cached in (0, 130, 201):                                 # tokens of the context that earlier steps brought
+        for window, query, far, visible in cases:
+            if query < cached:
+                continue
+            setup = paged_setup(dtype, [length], [length - cached], heads, kv_heads, head_dim, block_size,
+                                seed=query + far + cached)
+            q = setup["q"].float()
+            row = query - cached
+            key = 9.0 * q[row, 1] / q[row, 1].norm()
+            block = int(setup["table"][0, far // block_size])
+            setup["k_cache"][block, 0, far % block_size] = key.to(dtype)
+            setup["keys"][0][far, 0] = key.cpu()
+            n = length - cached
+            out = torch.zeros(n, heads * head_dim, device="cuda").to(dtype)
+            cu_q = torch.tensor([0, n], dtype=torch.int32, device="cuda")
+            ctx_after = torch.tensor([length], dtype=torch.int32, device="cuda")
+            k.attention_prefill_tc(setup["q"].view(n, -1).contiguous(), setup["k_cache"], setup["v_cache"],
+                                   setup["table"], cu_q, ctx_after, out, n, heads, kv_heads, head_dim, block_size,
+                                   4.0, window)
+            ref = attention_reference(setup, dtype, heads, kv_heads, 4.0, window).view(n, -1)
+            close(out, ref, dtype)
+            got = out[row, head_dim:].float().cpu()
+            want = setup["values"][0][far, 0].to(dtype).float()
+            assert torch.allclose(got, want, rtol=2e-2, atol=2e-2) == visible, (cached, window, query, far)
+    torch.cuda.synchronize()
+    assert int(k.error_flag.item()) == 0

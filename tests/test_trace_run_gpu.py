@@ -11,12 +11,11 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_replay_three_ways(tmp_path, dtype, name):
-    folder = make_folder(tmp_path / "model", TINY[name], seed=21)
+    folder = make_folder(tmp_path / "model", TINY[name], seed=21, dtype=dtype)
     config, weights = plain_llama.load_folder(folder)
     vocab = TINY[name]["vocab_size"]
     requests = {f"r{i}": random_tokens(vocab, n, seed=200 + i) for i, n in enumerate((40, 33, 75))}
     ref = {k: plain_llama.logits_of(config, weights, v).numpy() for k, v in requests.items()}
-    rtol, atol = tolerance(dtype)
     steps, expect = [], {}
     # (1) each request alone and whole
     for ident, tokens in requests.items():
@@ -52,4 +51,5 @@ def test_replay_three_ways(tmp_path, dtype, name):
     got = run_trace(folder, dtype, steps, tmp_path / "out", max_tokens=64 * 2 * 3)
     assert set(got) == set(expect)
     for step, want in expect.items():
+        rtol, atol = tolerance(dtype, want)
         np.testing.assert_allclose(got[step], want, rtol=rtol, atol=atol, err_msg=f"step {step}")

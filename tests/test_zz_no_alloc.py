@@ -58,7 +58,8 @@ def test_no_alloc_entry_point_matches_the_regular_one_twice():
                      3, heads, kv_heads, head_dim, block_size, ctypes.c_float(scale), 0, splits, stream)
         assert code == 0, lib.skv_last_error().decode()
         torch.cuda.synchronize()
-        torch.testing.assert_close(got.float(), expected.float(), rtol=1.6e-2, atol=1e-2)
+        # the same two kernels with the same splits, only the scratch lies elsewhere: the same bits
+        assert torch.equal(got, expected)
     # a request beyond the built-in array is refused, with both numbers in the message, and launches nothing
     too_many = int(capacity // (heads * (head_dim + 2))) + 1
     code = entry(ptr(q), ptr(k_cache), ptr(v_cache), ptr(table), table.shape[1], ptr(ctx_after), ptr(got),
