@@ -217,10 +217,127 @@ def prefill_flops(config, tokens):
     return linear + attention
 
 
-def reference_arm():
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "pip cannot install the reference: it is a CMake C++/CUDA project with neither setup.py "
-                      "nor pyproject.toml, and its kernels target sm_61"}))
+REFERENCE_SOURCE = Path("/root/reference")
+REFERENCE_BUILD = ROOT / "baseline" / "_ref" / "build"
+
+
+def reference_cli():
+    """Path of the reference's own ``stratakv_cli``, built unmodified out of tree with CMake for sm_100
+    (its architecture is a cache variable, CMakeLists.txt:31-33).  Its Release configuration hands MSVC
+    options to nvcc's host compiler on every platform (CMakeLists.txt:104-113), so the same optimisation
+    flags are given on the command line with no build type instead.  Returns (path, None) or (None, why)."""
+    import shutil
+    binary = REFERENCE_BUILD / "stratakv_cli"
+    if binary.is_file():
+        return binary, None
+    if not (REFERENCE_SOURCE / "CMakeLists.txt").is_file():
+        return None, "the reference's source tree is not on this machine and baseline/_ref/build holds no stratakv_cli"
+    cmake, nvcc = shutil.which("cmake"), shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not cmake or not Path(nvcc).is_file():
+        return None, "cmake or nvcc is missing: the reference cannot be built here"
+    cuda_include = str(Path(nvcc).resolve().parent.parent / "include")
+    configure = [cmake, "-S", str(REFERENCE_SOURCE), "-B", str(REFERENCE_BUILD), "-G", "Ninja", "-DSTRATAKV_CUDA=ON",
+                 "-DCMAKE_CUDA_ARCHITECTURES=100", "-DBUILD_TESTING=OFF", "-DCMAKE_BUILD_TYPE=",
+                 f"-DCMAKE_CUDA_COMPILER={nvcc}", f"-DCMAKE_CXX_FLAGS=-O3 -mavx2 -mfma -DNDEBUG -I{cuda_include}",
+                 "-DCMAKE_CUDA_FLAGS=-O3 --use_fast_math -Xptxas=-O3 -DNDEBUG"]
+    for command in (configure, [cmake, "--build", str(REFERENCE_BUILD), "--target", "stratakv_cli", "-j", "8"]):
+        done = subprocess.run(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if done.returncode != 0:
+            return None, "building the reference with CMake failed: " + done.stdout.strip().splitlines()[-1][:200]
+    return (binary, None) if binary.is_file() else (None, "the CMake build left no stratakv_cli")
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference on the same workload, through its stock path: ``stratakv_cli
+    <model.safetensors> <max_new_tokens> <ids...>`` (src/cli.cpp:179-322), one sequence per process, the way
+    its own benchmark.py drives it.  The reference runs one sequence at a time and takes a prompt one token
+    per step, so the batch of 8 becomes 8 runs one after another.  Its only timer covers prompt and
+    decoding together (src/generation/generator.cpp:635, 800-801), so each sequence runs twice: with 1 new
+    token and with 1 + steps; the difference of the two ``gen_ms`` is the time of ``steps`` decode steps
+    whose context ends at 2,048.  Nothing of this repo's kernels or engine is used; only the safetensors
+    writer makes the random checkpoint."""
+    import re
+    import shutil
+    import tempfile
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.shape != "tinyllama-1.1b":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm runs the headline shape only"}))
+        return 0
+    cli, why = reference_cli()
+    if cli is None:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    import torch
+    from stratakv_b200.config import LlamaConfig
+    from stratakv_b200.weights import write_random_model
+    steps, sequences = max(args.steps, 1), args.batch
+    shape = dict(SHAPES[args.shape], num_hidden_layers=args.layers or SHAPES[args.shape]["num_hidden_layers"])
+    prompt_length = CONTEXT - steps
+    work = Path(tempfile.mkdtemp(prefix="skv_reference_"))
+    pattern = re.compile(r"\[TIMING\].*?load_ms = ([0-9.eE+-]+), gen_ms = ([0-9.eE+-]+), tokens = (\d+)")
+
+    def run(prompt, new_tokens):
+        command = [str(cli), str(work / "model.safetensors"), str(new_tokens)] + [str(t) for t in prompt]
+        try:
+            done = subprocess.run(command, capture_output=True, text=True, timeout=900)
+        except subprocess.TimeoutExpired:
+            raise RuntimeError("the reference's stratakv_cli did not finish one sequence within 900 s")
+        found = pattern.search(done.stderr)
+        if done.returncode != 0 or not found:
+            raise RuntimeError(f"the reference's stratakv_cli exited with {done.returncode}: "
+                               + (done.stderr.strip().splitlines() or ["no output"])[-1][:200])
+        return float(found.group(2)), int(found.group(3)), float(found.group(1))
+
+    try:
+        write_random_model(work, LlamaConfig.from_dict(shape), seed=0, dtype=torch.bfloat16)
+        sampler = ClockSampler()
+        sampler.start()
+        decode_ms, decoded, per_sequence, prompt_ms, load_ms = 0.0, 0, [], [], []
+        for index in range(sequences):
+            prompt = random_ids(prompt_length, shape["vocab_size"], 1000 + index)
+            short_ms, short_tokens, _ = run(prompt, 1)
+            long_ms, long_tokens, loaded = run(prompt, 1 + steps)
+            decode_ms += long_ms - short_ms
+            decoded += long_tokens - short_tokens
+            per_sequence.append((long_tokens - short_tokens) * 1000.0 / max(long_ms - short_ms, 1e-9))
+            prompt_ms.append(short_ms)
+            load_ms.append(loaded)
+        clocks = sampler.stop()
+    except (RuntimeError, OSError) as error:
+        print(json.dumps({"impl": "reference", "unavailable": str(error)}))
+        return 0
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+    if decoded <= 0 or decode_ms <= 0:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference generated no tokens beyond the first "
+                          "(its greedy choice hit its end-of-sequence id 2)"}))
+        return 0
+    value = decoded * 1000.0 / decode_ms
+    vocab_bytes = shape["vocab_size"] * 4
+    print(json.dumps({
+        "metric": f"decode tokens/s ({args.shape} shape, bf16, batch {sequences}, context {CONTEXT})",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": sequences * 1000.0 / value, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
+        "config": {"model": f"{args.shape} shape", "layers": shape["num_hidden_layers"],
+                   "layers_of_model": SHAPES[args.shape]["num_hidden_layers"], "hidden": shape["hidden_size"],
+                   "heads": shape["num_attention_heads"], "kv_heads": shape["num_key_value_heads"],
+                   "head_dim": shape["head_dim"], "ffn": shape["intermediate_size"], "vocab": shape["vocab_size"],
+                   "global_batch": sequences, "seq_len": CONTEXT, "context_at_end": CONTEXT,
+                   "parallelism": "single GPU, one sequence at a time (the reference's stock path)",
+                   "timing": "difference of gen_ms of two stratakv_cli runs per sequence (1 and 1+steps new tokens)",
+                   "warm": f"the {prompt_length} prompt tokens, which the reference runs one per step, precede the timed steps",
+                   "cache_block": 16, "l2": "inputs larger than L2 (weights 2.1 GB per token)"},
+        "clocks": clocks,
+        # its stock path is end to end already: token ids come from the host, every step copies the logits to
+        # the host and samples there
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": vocab_bytes,
+                "prefill_ms": statistics.median(prompt_ms), "load_ms": statistics.median(load_ms)},
+        "prefill": {"value": prompt_length * 1000.0 / statistics.median(prompt_ms), "tokens": prompt_length,
+                    "ms": statistics.median(prompt_ms), "note": "the reference takes a prompt one token per step"},
+        "per_sequence_tokens_per_s": per_sequence, "gpu_launches": None, "impl": "reference"}))
     return 0
 
 
@@ -236,7 +353,7 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     args = parser.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -281,7 +398,7 @@ def main() -> int:
     result = {
         "metric": f"decode tokens/s ({args.shape} shape, bf16, batch {args.batch}, context {CONTEXT})",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": value / 33.8 if args.shape == "tinyllama-1.1b" else None,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
         "config": {"model": f"{args.shape} shape", "layers": args.layers, "layers_of_model": shape["num_hidden_layers"],
                    "hidden": config.hidden_size, "heads": config.num_attention_heads,
