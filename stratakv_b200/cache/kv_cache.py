@@ -26,16 +26,26 @@ import torch
 
 from ..parts.base import CacheRequest
 from .allocator import CacheFull, IdAllocator
+from .kinds import CacheKind, cache_kind
 
 
 @dataclass
 class CacheGroup:
     index: int
     request: CacheRequest
+    kind: CacheKind
     entries: List[int]                    # cache entry ids, in local order
     blocks: IdAllocator
-    keys: torch.Tensor | None = None      # [entries, blocks, kv_heads, block_size, head_dim]
-    values: torch.Tensor | None = None
+    # what the kind keeps, by tensor name: [entries, blocks + 1, *the kind's shape of one block]
+    storage: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+    @property
+    def keys(self) -> torch.Tensor:       # [entries, blocks, kv_heads, block_size, head_dim] for the "kv" kinds
+        return self.storage["k"]
+
+    @property
+    def values(self) -> torch.Tensor:
+        return self.storage["v"]
 
 
 @dataclass
@@ -59,26 +69,27 @@ class KVCache:
         self.entry_group: List[Tuple[int, int]] = []        # entry -> (group, local index); (-1, -1): none
         by_key: Dict[tuple, CacheGroup] = {}
         for entry, request in enumerate(requests):
-            if request.kind == "none":
+            try:
+                kind = cache_kind(request.kind)
+            except ValueError as error:
+                raise ValueError(f"cache entry {entry}: {error}") from None
+            if not kind.paged:
                 self.entry_group.append((-1, -1))
                 continue
-            if request.kind not in ("kv", "kv_window"):
-                raise ValueError(f"cache entry {entry}: unknown cache kind '{request.kind}'")
-            if request.kind == "kv_window" and request.window <= 0:
+            if kind.windowed and request.window <= 0:
                 raise ValueError(f"cache entry {entry}: a window group needs a positive window")
             group = by_key.get(request.group_key())
             if group is None:
-                group = CacheGroup(len(self.groups), request, [], IdAllocator(num_blocks, "block"))
+                group = CacheGroup(len(self.groups), request, kind, [], IdAllocator(num_blocks, "block"))
                 by_key[request.group_key()] = group
                 self.groups.append(group)
             self.entry_group.append((group.index, len(group.entries)))
             group.entries.append(entry)
         for group in self.groups:
             # one block more than the allocator hands out: padding rows of a step write there
-            shape = (len(group.entries), num_blocks + 1, group.request.num_kv_heads, block_size,
-                     group.request.head_dim)
-            group.keys = torch.zeros(shape, dtype=dtype, device=self.device)
-            group.values = torch.zeros(shape, dtype=dtype, device=self.device)
+            for name, shape in group.kind.block_tensors(group.request, block_size).items():
+                group.storage[name] = torch.zeros((len(group.entries), num_blocks + 1) + tuple(shape), dtype=dtype,
+                                                  device=self.device)
         # Fixed-size per-sequence state, one row per slot for each entry that asks for some.
         self.state_bytes = [r.state_bytes for r in requests]
         self._state = {entry: torch.zeros((max_slots, r.state_bytes), dtype=torch.uint8, device=self.device)
@@ -94,6 +105,13 @@ class KVCache:
             raise KeyError(f"cache entry {entry} keeps no keys")
         return self.groups[group].keys[local], self.groups[group].values[local]
 
+    def entry_storage(self, entry: int) -> Dict[str, torch.Tensor]:
+        """Every tensor the entry's cache kind keeps, by name: ``[blocks + 1, *shape of one block]``."""
+        group, local = self.entry_group[entry]
+        if group < 0:
+            raise KeyError(f"cache entry {entry} keeps nothing per position")
+        return {name: tensor[local] for name, tensor in self.groups[group].storage.items()}
+
     def entry_group_index(self, entry: int) -> int:
         return self.entry_group[entry][0]
 
@@ -102,9 +120,8 @@ class KVCache:
         return self._state[entry]
 
     def bytes_per_token(self) -> int:
-        width = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.request.num_kv_heads * g.request.head_dim * width
-                   for g in self.groups)
+        return sum(tensor[:, 0].numel() * tensor.element_size() // self.block_size
+                   for g in self.groups for tensor in g.storage.values())
 
     # ---- sequences ---------------------------------------------------------
     def acquire(self) -> int:
@@ -159,7 +176,7 @@ class KVCache:
         record = self.sequences[slot]
         record.length = new_length
         for group in self.groups:
-            if group.request.kind != "kv_window":
+            if not group.kind.windowed:
                 continue
             # The next query sits at position >= new_length and sees keys at
             # positions > position - window, so keys below new_length - window + 1 are dead.

@@ -84,6 +84,26 @@ inline int launch_pdl(const char* name, void (*kernel)(KernelArgs...), dim3 grid
     return 0;
 }
 
+// Number of SMs of the current device (asked once per process; a process drives one kind of GPU).
+inline int sm_count() {
+    static const int count = [] {
+        int device = 0, value = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || value <= 0)
+            value = 1;
+        return value;
+    }();
+    return count;
+}
+
+// Activations of a gated feed-forward's gate, chosen by the part's spec (ops.ACTIVATIONS has the names).
+enum { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_COUNT = 2 };
+
+// gelu(g) = g/2 * (1 + tanh(sqrt(2/pi) * (g + 0.044715 g^3))), the "tanh" form.
+__device__ __forceinline__ float gelu_tanh(float g) {
+    return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ float to_float(float v) { return v; }

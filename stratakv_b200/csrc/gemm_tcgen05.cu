@@ -132,12 +132,15 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
 // For very negative g the exponential overflows to infinity and the quotient is -0, the right limit.
 __device__ __forceinline__ float silu_gate(float g) { return g / (1.0f + expf(-g)); }
 
+// The gate's activation, chosen by the caller (common.cuh names them).
+__device__ __forceinline__ float gate_activation(float g, int act) { return act == ACT_GELU_TANH ? gelu_tanh(g) : silu_gate(g); }
+
 // The epilogue of one output tile for one of the four epilogue warps: reads the warp's quarter of the
 // accumulator (TMEM lanes 32*quarter .., one output row per thread) and stores it in the mode asked for.
 template <int BN>
 __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, int lane, uint8_t* slabs, int& buffer,
                                               const CUtensorMap* map_out, int tma_out, void* __restrict__ out, int M,
-                                              int N, int mode, int m0, int n0) {
+                                              int N, int mode, int act, int m0, int n0) {
     const int m = m0 + quarter * 32 + lane;
     if (tma_out) {
         // Each thread builds 128 bytes of its output row in a swizzled slab of shared memory; one lane
@@ -167,9 +170,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
                         uint32_t packed[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const float lo = silu_gate(__uint_as_float(v[16 * grp + 2 * j])) *
+                            const float lo = gate_activation(__uint_as_float(v[16 * grp + 2 * j]), act) *
                                              __uint_as_float(v[16 * grp + 8 + 2 * j]);
-                            const float hi = silu_gate(__uint_as_float(v[16 * grp + 2 * j + 1])) *
+                            const float hi = gate_activation(__uint_as_float(v[16 * grp + 2 * j + 1]), act) *
                                              __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
                             const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
                             packed[j] = *(const uint32_t*)&pair;
@@ -225,9 +228,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
                         uint32_t packed[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const float lo = silu_gate(__uint_as_float(v[16 * grp + 2 * j])) *
+                            const float lo = gate_activation(__uint_as_float(v[16 * grp + 2 * j]), act) *
                                              __uint_as_float(v[16 * grp + 8 + 2 * j]);
-                            const float hi = silu_gate(__uint_as_float(v[16 * grp + 2 * j + 1])) *
+                            const float hi = gate_activation(__uint_as_float(v[16 * grp + 2 * j + 1]), act) *
                                              __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
                             const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
                             packed[j] = *(const uint32_t*)&pair;
@@ -286,7 +289,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
-                    int N, int K, int mode, int* __restrict__ flag) {
+                    int N, int K, int mode, int act, int* __restrict__ flag) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     constexpr uint32_t SLAB_BYTES = 4 * 2 * 4096;           // four epilogue warps, two 32 x 128-byte slabs each
     extern __shared__ uint8_t smem_raw[];
@@ -384,7 +387,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
             epilogue_tile<BN>(tmem_base + (uint32_t)(buf * BN), quarter, lane, slabs, buffer, &map_out, tma_out, out, M, N,
-                              mode, m0, n0);
+                              mode, act, m0, n0);
             // the accumulator has been read out: hand it back to the issuer
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -415,7 +418,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int MP, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                               void* __restrict__ out, int M, int N, int K, int mode, int splits,
+                               void* __restrict__ out, int M, int N, int K, int mode, int act, int splits,
                                int* __restrict__ flag) {
     constexpr uint32_t W_BYTES = 128 * TC_BK * 2, X_BYTES = MP * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -557,7 +560,7 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
                     const float up = __shfl_down_sync(0xffffffffu, __uint_as_float(v[j]), 8);
                     if ((lane & 8) == 0 && c + j < M && n < N)
                         ((__nv_bfloat16*)out)[(size_t)(c + j) * half_n + o] =
-                            __float2bfloat16_rn(silu_gate(__uint_as_float(v[j])) * up);
+                            __float2bfloat16_rn(gate_activation(__uint_as_float(v[j]), act) * up);
                 }
             } else if (n < N) {
                 if (mode == TC_MODE_STORE) {
@@ -656,7 +659,7 @@ static int tensor_map(const void* base, int rows, int cols, int elem_bytes, int 
 }
 
 template <int BN, int STAGES>
-static int launch_tc(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
+static int launch_tc(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
                      cudaStream_t stream) {
     CUtensorMap map_a, map_w, map_out;
     if (int code = tensor_map(a, M, K, 2, TC_BM, TC_BK, &map_a)) return code;
@@ -691,12 +694,12 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
     dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));     // one persistent block per SM at most
     return launch_pdl("skv_linear(tcgen05)", gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(TC_THREADS), smem, stream,
-                      map_a, map_w, map_out, tma_out, out, M, N, K, mode, flag);
+                      map_a, map_w, map_out, tma_out, out, M, N, K, mode, act, flag);
 }
 
 template <int MP, int STAGES>
-static int launch_few_tokens(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
-                             cudaStream_t stream) {
+static int launch_few_tokens(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
+                             int* flag, cudaStream_t stream) {
     CUtensorMap map_w, map_x;
     if (int code = tensor_map(w, N, K, 2, 128, TC_BK, &map_w)) return code;
     if (int code = tensor_map(a, M, K, 2, MP, TC_BK, &map_x)) return code;
@@ -736,23 +739,23 @@ static int launch_few_tokens(const void* a, const void* w, void* out, int M, int
     config.attrs = attributes;
     config.numAttrs = pdl_enabled() ? 2 : 1;
     const cudaError_t status = cudaLaunchKernelEx(&config, gemm_tcgen05_few_tokens_kernel<MP, STAGES>, map_w, map_x, out,
-                                                  M, N, K, mode, splits, flag);
+                                                  M, N, K, mode, act, splits, flag);
     if (status != cudaSuccess) return fail("skv_linear(tcgen05)", cudaGetErrorString(status));
     return 0;
 }
 
-int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
+int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
                    cudaStream_t stream) {
     if (K % 8 != 0) return fail("skv_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_linear(tcgen05)", "operands must be 16-byte aligned");
     if (mode == TC_MODE_GATED && N % 16 != 0) return fail("skv_linear(tcgen05)", "a gated weight needs a multiple of 16 rows");
-    if (M <= 32) return launch_few_tokens<32, 8>(a, w, out, M, N, K, mode, flag, stream);
-    if (M <= 64) return launch_few_tokens<64, 8>(a, w, out, M, N, K, mode, flag, stream);
-    if (M <= 128) return launch_few_tokens<128, 6>(a, w, out, M, N, K, mode, flag, stream);
+    if (M <= 32) return launch_few_tokens<32, 8>(a, w, out, M, N, K, mode, act, flag, stream);
+    if (M <= 64) return launch_few_tokens<64, 8>(a, w, out, M, N, K, mode, act, flag, stream);
+    if (M <= 128) return launch_few_tokens<128, 6>(a, w, out, M, N, K, mode, act, flag, stream);
     // Wider tiles re-read less of A and W from L2 per flop; narrow ones waste less on small N.
     if (N > 128 && (long long)((M + 127) / 128) * ((N + 255) / 256) >= 96)
-        return launch_tc<256, 4>(a, w, out, M, N, K, mode, flag, stream);
-    return launch_tc<128, 4>(a, w, out, M, N, K, mode, flag, stream);
+        return launch_tc<256, 4>(a, w, out, M, N, K, mode, act, flag, stream);
+    return launch_tc<128, 4>(a, w, out, M, N, K, mode, act, flag, stream);
 }
 
 }  // namespace skv

@@ -24,12 +24,11 @@
 namespace skv {
 
 enum { MODE_STORE = 0, MODE_STORE_F32 = 1, MODE_ADD_F32 = 2, MODE_GATED = 3 };
-enum { ACT_SILU = 0 };
 
 __device__ __forceinline__ float activate(float g, int act) {
+    if (act == ACT_GELU_TANH) return gelu_tanh(g);
     // silu(g) = g * sigmoid(g); the two-branch sigmoid of the reference's CPU
     // block (src/models/transformer_block.cpp:315-323) avoids overflow of exp.
-    (void)act;
     const float sig = g >= 0.0f ? 1.0f / (1.0f + expf(-g)) : expf(g) / (1.0f + expf(g));
     return g * sig;
 }
@@ -363,12 +362,13 @@ static int launch_skinny(const void* a, const void* w, void* out, int M, int N, 
     const int row_tiles = (N + 15) / 16, chunks = (M + 8 * TG - 1) / (8 * TG);
     const int steps = (K + 31) / 32;
     const long long blocks = (long long)row_tiles * chunks;
-    int warps = blocks >= 148 * 4 ? 4 : 8;
+    const int sms = sm_count();
+    int warps = blocks >= sms * 4 ? 4 : 8;
     // A few more tiles than five blocks of 4 warps per SM hold (768 at hidden size 4096) would leave a second,
     // nearly empty wave that doubles the time; blocks of 3 warps (96 registers a thread) fit 7 to an SM.  (Blocks
     // of 2 warps or 1, of which 10 or 21 fit, measured slower than two waves.)
-    if (TG <= 2 && blocks > 148 * 5 && blocks <= 148 * 7) warps = 3;
-    if (warps == 8 && MAX_WARPS >= 16 && steps > 8 * U * 2 && blocks <= 148) warps = 16;   // (16 warps: one block per SM)
+    if (TG <= 2 && blocks > sms * 5 && blocks <= sms * 7) warps = 3;
+    if (warps == 8 && MAX_WARPS >= 16 && steps > 8 * U * 2 && blocks <= sms) warps = 16;   // (16 warps: one block per SM)
     if (warps > MAX_WARPS) warps = MAX_WARPS;
     while (warps > 1 && warps > steps) warps >>= 1;
     if (warps <= 4) return launch_skinny_as<TG, U, 4>(a, w, out, M, N, K, mode, act, warps, norm, stream);
@@ -377,16 +377,8 @@ static int launch_skinny(const void* a, const void* w, void* out, int M, int N, 
 }
 
 // gemm_tcgen05.cu: the tensor-memory GEMM that serves steps with many tokens
-int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int* flag,
+int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
                    cudaStream_t stream);
-
-static bool tcgen05_enabled() {
-    static const bool enabled = [] {
-        const char* off = getenv("SKV_NO_TCGEN05");
-        return !(off && off[0] == '1');
-    }();
-    return enabled;
-}
 
 static int launch_linear(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                          int* flag, const NormArgs& norm, cudaStream_t stream) {
@@ -397,8 +389,8 @@ static int launch_linear(const void* a, const void* w, void* out, int M, int N, 
     if ((norm.row_scale || norm.partials_in || norm.partials) && M > 64)
         return fail("skv_linear(bfloat16)", "the norm-fused form serves steps of at most 64 tokens");
     // above 16 tokens the tensor-memory kernels take over, unless a norm is folded into this projection
-    if (M > 16 && !norm.row_scale && !norm.partials_in && !norm.partials && tcgen05_enabled())
-        return linear_tcgen05(a, w, out, M, N, K, mode, flag, stream);
+    if (M > 16 && !norm.row_scale && !norm.partials_in && !norm.partials)
+        return linear_tcgen05(a, w, out, M, N, K, mode, act, flag, stream);
     // at most 8 warps and under 100 registers a thread: two blocks fit on an SM, so the next
     // kernel's weight loads are in flight while this one finishes
     if (M <= 8) return launch_skinny<1, 8, 16>(a, w, out, M, N, K, mode, act, norm, stream);
@@ -417,7 +409,7 @@ static int check_linear(int M, int N, int K, int mode, int act) {
     if (mode < 0 || mode > 3) return fail("skv_linear", "unknown epilogue mode");
     if (mode == MODE_GATED && N % 16 != 0)
         return fail("skv_linear", "a gated weight must have a multiple of 16 rows (gate/up tiles of 8)");
-    if (act != ACT_SILU) return fail("skv_linear", "unknown activation");
+    if (act < 0 || act >= ACT_COUNT) return fail("skv_linear", "unknown activation");
     (void)M;
     return 0;
 }

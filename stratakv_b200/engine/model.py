@@ -31,14 +31,12 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorRequest]:
                                  f"{found[name].shape} and {request.shape}")
             found.setdefault(name, request)
 
-    add({spec.embedding.weight: TensorRequest((spec.embedding.vocab_size, spec.embedding.hidden_size))})
+    add(part_class("embedding", spec.embedding.kind).expected_tensors(spec.embedding))
     for layer in spec.layers:
-        add(part_class("norm", layer.mixer_norm.kind).expected_tensors(layer.mixer_norm))
-        add(part_class("mixer", layer.mixer.kind).expected_tensors(layer.mixer))
-        add(part_class("norm", layer.ffn_norm.kind).expected_tensors(layer.ffn_norm))
-        add(part_class("ffn", layer.ffn.kind).expected_tensors(layer.ffn))
+        for _, role, part_spec in layer.named_parts():
+            add(part_class(role, part_spec.kind).expected_tensors(part_spec))
     add(part_class("norm", spec.final_norm.kind).expected_tensors(spec.final_norm))
-    add({spec.head.weight: TensorRequest((spec.head.vocab_size, spec.head.hidden_size))})
+    add(part_class("head", spec.head.kind).expected_tensors(spec.head))
     return found
 
 
@@ -52,7 +50,8 @@ def cache_requests(spec: ModelSpec) -> List[CacheRequest]:
             if requests[entry.cache] is not None:
                 raise ValueError(f"cache entry {entry.cache} is written by two runs")
             mixer = spec.layers[entry.layer].mixer
-            requests[entry.cache] = part_class("mixer", mixer.kind).cache_request(mixer)
+            requests[entry.cache] = (part_class("mixer", mixer.kind).cache_request(mixer) if mixer is not None
+                                     else CacheRequest())
     for index, request in enumerate(requests):
         if request is None:
             raise ValueError(f"cache entry {index} is read but no run writes it")
@@ -73,28 +72,22 @@ class Model:
         self.rt = runtime
         self.layers = [Layer(layer_spec, runtime) for layer_spec in spec.layers]
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, runtime)
-        self.embedding = None
-        self.head = None
+        self.embedding = part_class("embedding", spec.embedding.kind)(spec.embedding, runtime)
+        self.head = part_class("head", spec.head.kind)(spec.head, runtime)
         # Raised by kernels: bit 0 = token id outside the vocabulary.
         self.flags = torch.zeros(1, dtype=torch.int32, device=runtime.device)
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        uploaded: Dict[str, torch.Tensor] = {}
-
-        def table(name):
-            if name not in uploaded:
-                uploaded[name] = self.rt.upload(tensors[name])
-            return uploaded[name]
-
-        self.embedding = table(self.spec.embedding.weight)
-        self.head = table(self.spec.head.weight)          # the same tensor when tied
+        self.embedding.bind(tensors)
+        self.head.bind(tensors)                            # the same device tensor when tied
         for layer in self.layers:
             for part in layer.parts():
                 part.bind(tensors)
         self.final_norm.bind(tensors)
 
     def graph_safe(self) -> bool:
-        return all(part.graph_safe for layer in self.layers for part in layer.parts()) and self.final_norm.graph_safe
+        return (all(part.graph_safe for layer in self.layers for part in layer.parts())
+                and self.final_norm.graph_safe and self.embedding.graph_safe and self.head.graph_safe)
 
     def prepare_positions(self, max_positions: int) -> None:
         """Let position encodings build their tables up to ``max_positions`` (before a graph capture)."""
@@ -106,12 +99,12 @@ class Model:
     def weight_bytes(self) -> int:
         """Bytes of weights one decode step reads (each matrix once; one embedding row per token is left out)."""
         seen, total = set(), 0
-        tensors = [self.head, self.final_norm.gamma] if hasattr(self.final_norm, "gamma") else [self.head]
-        for layer in self.layers:
-            for part in layer.parts():
-                for value in vars(part).values():
-                    if isinstance(value, torch.Tensor):
-                        tensors.append(value)
+        tensors = []
+        parts = [self.head, self.final_norm] + [part for layer in self.layers for part in layer.parts()]
+        for part in parts:
+            for value in vars(part).values():
+                if isinstance(value, torch.Tensor):
+                    tensors.append(value)
         for tensor in tensors:
             if tensor.data_ptr() not in seen:
                 seen.add(tensor.data_ptr())
@@ -126,27 +119,24 @@ class Model:
 
     def _forward(self, step: StepBatch, want_rows: Optional[torch.Tensor], n_want: int):
         rt, spec = self.rt, self.spec
-        ops = rt.kernels()
         x = rt.workspace.get("residual", (step.n_tokens, spec.hidden_size), torch.float32)
         stats = None
         if step.is_decode and rt.dtype == torch.bfloat16 and step.n_tokens <= MAX_FUSED_ROWS:
             # few rows: norms are folded into the projections after them (residual.py)
             stats = ResidualStats.allocate(rt.workspace.get, step.n_tokens, spec.hidden_size, rt.dtype)
         step.residual_stats = stats
-        final = self.final_norm if self.final_norm.folds_norm else None
+        final = self.final_norm if self.final_norm.folds_norm and self.head.folds_norm else None
         readers = [self.layers[entry.layer].first_norm for entry in spec.schedule] + [final]
         if stats is not None:
             stats.expect(readers[0])
-        ops.embed(self.embedding, step.token_ids, x, self.flags, stats=stats)
+        self.embedding.forward(step, x, self.flags, stats=stats)
         for index, entry in enumerate(spec.schedule):
             step.norm_after_layer = readers[index + 1]
             self.layers[entry.layer].forward(step, x, entry)
         if n_want == 0:
             return None
-        if stats is not None and self.final_norm.folds_norm:
+        if stats is not None and final is not None:
             y = self.final_norm.forward(x, rows=want_rows, name="final_normed", stats=stats)
         else:
             y = self.final_norm.forward(x, rows=want_rows, name="final_normed")
-        logits = rt.workspace.get("logits", (n_want, spec.vocab_size), torch.float32)
-        ops.linear(y, self.head, logits, _ops.MODE_STORE_F32)
-        return logits
+        return self.head.forward(y, n_want)

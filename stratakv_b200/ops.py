@@ -15,7 +15,8 @@ from .csrc.build import BuildError, build_library
 from .residual import COLUMNS_PER_PARTIAL, KERNEL_FOLD_ROWS, NormedRows
 
 MODE_STORE, MODE_STORE_F32, MODE_ADD_F32, MODE_GATED = 0, 1, 2, 3
-ACTIVATIONS = {"silu": 0, "swish": 0}
+# activations of a gated feed-forward's gate that every projection kernel implements (csrc/common.cuh)
+ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1}
 _DTYPE_NAMES = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
 
 

@@ -17,7 +17,7 @@ from .base import CacheRequest, Mixer, TensorRequest
 from .registry import part_class, register_mixer
 
 
-def decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148) -> int:
+def decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int) -> int:
     """Into how many pieces a decode step cuts each context: enough blocks to fill the
     GPU twice over, at least 128 keys (one group of 16 per warp) a piece.  It depends on
     the step's sizes only, never on which sequences are live."""
@@ -26,7 +26,7 @@ def decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148
     return max(1, min(by_length, by_count, 64))
 
 
-def fused_decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int = 148, per_sm: int = 2) -> int:
+def fused_decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int, per_sm: int = 2) -> int:
     """The same for the fused kernel, whose pieces are the blocks of one cluster: the largest
     power of two (other cluster sizes measured slower), at most 8, that keeps the grid within
     ``per_sm`` blocks per SM (2 up to head size 64, 1 above: the staged keys of a block take
@@ -41,7 +41,7 @@ def fused_decode_splits(n_seqs: int, blocks_per_seq: int, max_ctx: int, sms: int
     return wanted
 
 
-def wants_more_pieces(n_seqs: int, blocks_per_seq: int, max_ctx: int, cluster_splits: int, sms: int = 148) -> bool:
+def wants_more_pieces(n_seqs: int, blocks_per_seq: int, max_ctx: int, cluster_splits: int, sms: int) -> bool:
     """A cluster holds at most 8 pieces of a context.  Few long sequences want more: when the fused kernel's
     grid leaves SMs idle, its pieces are 2,048 keys or longer and the path through scratch memory would cut
     at least twice as many (batch 1 at 32,000 keys: 1.14 ms a step with 64 pieces and a combine kernel,
@@ -103,8 +103,8 @@ class PagedAttention(Mixer):
         fused = (step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table")
                  and ops.has_attention_decode_fused())
         if fused:
-            splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx, per_sm=2 if s.head_dim <= 64 else 1)
-            fused = not wants_more_pieces(n, blocks_per_seq, step.max_ctx, splits)
+            splits = fused_decode_splits(n, blocks_per_seq, step.max_ctx, rt.sm_count, per_sm=2 if s.head_dim <= 64 else 1)
+            fused = not wants_more_pieces(n, blocks_per_seq, step.max_ctx, splits, rt.sm_count)
         if fused:
             # one kernel: rotation, cache write, attention over the context in up to 8 pieces, merge
             ops.attention_decode_fused(qkv, self.position.fusion_table(step.max_ctx), k_cache, v_cache, table,
@@ -116,7 +116,7 @@ class PagedAttention(Mixer):
         self.position.rotate_and_store(step, qkv, q, k_cache, v_cache, table, s.num_heads, s.num_kv_heads,
                                        s.head_dim, step.cache.block_size, writes_cache)
         if step.is_decode and rt.dtype == torch.bfloat16:
-            splits = decode_splits(n, blocks_per_seq, step.max_ctx)
+            splits = decode_splits(n, blocks_per_seq, step.max_ctx, rt.sm_count)
             scratch_o = scratch_ml = None
             if splits > 1:
                 scratch_o = rt.workspace.get("attn_split_o", (n * s.num_heads * splits * s.head_dim,), torch.float32)

@@ -31,8 +31,11 @@ class TensorRequest:
 class CacheRequest:
     """What one run of a mixer needs from the cache.
 
-    ``kind`` ``"kv"`` keeps every key and value; ``"kv_window"`` needs only the
-    last ``window``; ``"none"`` keeps no keys.  ``state_bytes`` is fixed-size
+    ``kind`` names a registered cache kind (``cache/kinds.py``): ``"kv"`` keeps
+    every key and value; ``"kv_window"`` needs only the last ``window``;
+    ``"none"`` keeps nothing per position.  ``v_head_dim`` is the width of a
+    value where it differs from a key's (0: the same); ``extra`` carries sizes
+    that a kind registered elsewhere wants.  ``state_bytes`` is fixed-size
     per-sequence state (zeroed when a sequence takes its slot).  Runs whose
     requests are equal share one group of storage."""
     kind: str = "none"
@@ -40,9 +43,11 @@ class CacheRequest:
     head_dim: int = 0
     window: int = 0
     state_bytes: int = 0
+    v_head_dim: int = 0
+    extra: Tuple[int, ...] = ()
 
     def group_key(self):
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.v_head_dim, self.extra)
 
 
 class Runtime:
@@ -54,6 +59,16 @@ class Runtime:
         self.workspace = workspace
         self._kernel_loader = kernel_loader          # (dtype, head_dim) -> kernels object
         self.default_head_dim = default_head_dim
+        self._sm_count = None
+        self._shared = {}                            # checkpoint tensor name -> its one copy on the device
+
+    @property
+    def sm_count(self) -> int:
+        """SMs of the device the model runs on (parts size their grids by it); 1 off the GPU."""
+        if self._sm_count is None:
+            self._sm_count = (torch.cuda.get_device_properties(self.device).multi_processor_count
+                              if self.device.type == "cuda" else 1)
+        return self._sm_count
 
     def kernels(self, head_dim: Optional[int] = None):
         """The kernel library; attention parts name their head size, others take any build."""
@@ -64,6 +79,13 @@ class Runtime:
         compute dtype).  float32 -> bfloat16 rounds to nearest even; the
         reference truncates (``src/cuda/gemm_cuda.cu:74-83``)."""
         return tensor.to(device=self.device, dtype=dtype or self.dtype).contiguous()
+
+    def upload_shared(self, name: str, tensor: torch.Tensor) -> torch.Tensor:
+        """``upload`` for a checkpoint tensor that several parts may name (tied embedding and head):
+        the first caller uploads it, the others get the same device tensor."""
+        if name not in self._shared:
+            self._shared[name] = self.upload(tensor)
+        return self._shared[name]
 
 
 @dataclass

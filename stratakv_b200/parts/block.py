@@ -16,14 +16,21 @@ class Layer:
 
     def __init__(self, spec, runtime):
         self.spec = spec
-        self.mixer_norm = part_class("norm", spec.mixer_norm.kind)(spec.mixer_norm, runtime)
-        self.mixer = part_class("mixer", spec.mixer.kind)(spec.mixer, runtime)
-        self.ffn_norm = part_class("norm", spec.ffn_norm.kind)(spec.ffn_norm, runtime)
-        self.ffn = part_class("ffn", spec.ffn.kind)(spec.ffn, runtime)
+        self.mixer_norm = self.mixer = self.ffn_norm = self.ffn = None
+        self.extra = {}
+        self._parts = []
+        named = {"mixer_norm", "mixer", "ffn_norm", "ffn"}
+        for name, role, part_spec in spec.named_parts():
+            part = part_class(role, part_spec.kind)(part_spec, runtime)
+            if name in named:
+                setattr(self, name, part)
+            else:
+                self.extra[name] = part
+            self._parts.append(part)
         self.run = part_class("arrangement", spec.arrangement)
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        return tuple(self._parts)
 
     def forward(self, step, x, entry):
         self.run(self, step, x, entry)
@@ -38,10 +45,12 @@ def _normed(norm, consumer, step, x):
 
 def foldable(norm, consumer):
     """The norm, if it can be folded into its consumer's first projection, else None."""
-    return norm if norm is not None and norm.folds_norm and consumer.folds_norm else None
+    return norm if norm is not None and consumer is not None and norm.folds_norm and consumer.folds_norm else None
 
 
 def pre_norm(layer: Layer, step, x, entry) -> None:
+    if layer.mixer_norm is None or layer.mixer is None or layer.ffn_norm is None or layer.ffn is None:
+        raise ValueError("the pre_norm arrangement needs a norm and a mixer, and a norm and a feed-forward")
     stats = step.residual_stats
     h = _normed(layer.mixer_norm, layer.mixer, step, x)
     if stats is not None:

@@ -1,6 +1,6 @@
 """Registries of part kinds: a spec's ``kind`` string chooses the class that runs it.
 
-A new mixer, feed-forward, norm or position encoding is added by registering
+A new mixer, feed-forward, norm, position encoding, embedding or output head is added by registering
 its class under a new kind; the model builder, the cache and the step function
 only see the interfaces in ``parts/base.py``.
 """
@@ -9,7 +9,7 @@ from __future__ import annotations
 from typing import Dict
 
 _KINDS: Dict[str, Dict[str, type]] = {"mixer": {}, "ffn": {}, "norm": {}, "position": {},
-                                      "arrangement": {}}
+                                      "arrangement": {}, "embedding": {}, "head": {}}
 
 
 def register_part(role: str, kind: str, cls) -> None:
@@ -23,6 +23,8 @@ def register_ffn(kind, cls): register_part("ffn", kind, cls)
 def register_norm(kind, cls): register_part("norm", kind, cls)
 def register_position(kind, cls): register_part("position", kind, cls)
 def register_arrangement(kind, fn): register_part("arrangement", kind, fn)
+def register_embedding(kind, cls): register_part("embedding", kind, cls)
+def register_head(kind, cls): register_part("head", kind, cls)
 
 
 def part_class(role: str, kind: str):

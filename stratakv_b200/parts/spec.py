@@ -65,12 +65,24 @@ class LayerSpec:
 
     ``pre_norm``: ``x += mixer(norm1(x)); x += ffn(norm2(x))``
     (``src/models/transformer_block.cpp:301-331``).
+
+    The four named places are what that arrangement uses; another arrangement may leave
+    some of them ``None`` (a block without a feed-forward, one norm for two branches) and
+    may name further parts in ``extras`` as ``(name, role, spec)``, which the layer builds
+    and hands to the arrangement as ``layer.extra[name]``.
     """
     mixer_norm: Any
     mixer: Any
-    ffn_norm: Any
-    ffn: Any
+    ffn_norm: Any = None
+    ffn: Any = None
     arrangement: str = "pre_norm"
+    extras: Tuple[Tuple[str, str, Any], ...] = ()
+
+    def named_parts(self):
+        """``(name, role, spec)`` of every part this layer has, in a fixed order."""
+        places = (("mixer_norm", "norm", self.mixer_norm), ("mixer", "mixer", self.mixer),
+                  ("ffn_norm", "norm", self.ffn_norm), ("ffn", "ffn", self.ffn))
+        return tuple(place for place in places if place[2] is not None) + tuple(self.extras)
 
 
 @dataclass(frozen=True)

@@ -140,3 +140,27 @@ def test_random_traffic_never_loses_a_block():
     for slot in list(live):
         cache.release(slot)
     assert cache.all_free()
+
+
+def test_a_cache_kind_registered_elsewhere_gets_its_own_storage():
+    """What a block holds is the cache kind's business: a kind registered by the test keeps one narrow
+    tensor per position instead of keys and values, beside ordinary layers whose values are wider than
+    their keys; the allocator, the slots and the block tables do not change."""
+    from stratakv_b200.cache import CacheKind, register_cache_kind
+    register_cache_kind(CacheKind("toy_latent", paged=True, windowed=False,
+                                  block_tensors=lambda request, block_size: {"latent": (block_size, request.extra[0])}))
+    requests = [CacheRequest("kv", 2, 16, v_head_dim=40), CacheRequest("toy_latent", extra=(24,)),
+                CacheRequest("toy_latent", extra=(24,)), CacheRequest("none", state_bytes=8)]
+    cache = KVCache(requests, 6, 16, 3, torch.bfloat16, "cpu")
+    assert len(cache.groups) == 2 and cache.entry_group == [(0, 0), (1, 0), (1, 1), (-1, -1)]
+    k, v = cache.entry_kv(0)
+    assert k.shape == (7, 2, 16, 16) and v.shape == (7, 2, 16, 40)
+    assert set(cache.entry_storage(2)) == {"latent"} and cache.entry_storage(2)["latent"].shape == (7, 16, 24)
+    assert cache.bytes_per_token() == 2 * (2 * 16 + 2 * 40) + 2 * 2 * 24
+    slot = cache.acquire()
+    cache.reserve({slot: 40})
+    assert cache.free_blocks() == [3, 3]
+    cache.release(slot)
+    assert cache.all_free()
+    with pytest.raises(ValueError, match="unknown cache kind 'nothing_like_it'"):
+        KVCache([CacheRequest("nothing_like_it")], 4, 16, 2, torch.float32, "cpu")

@@ -96,22 +96,26 @@ def test_few_rows_let_the_consumer_add_the_partial_sums():
     assert not ResidualStats(torch.zeros(16, 64), torch.zeros(16), torch.zeros(16, 512), torch.zeros(1, dtype=torch.int32)).consumer_sums
 
 
+SMS = 148        # the SM count is an argument of the policies; the engine passes the device's own
+
+
 def test_context_splits_depend_on_sizes_only():
     for batch in (1, 2, 3, 5, 8, 12, 16, 24, 32, 48, 64, 200):
         for groups in (1, 4, 8, 32):
             for ctx in (16, 100, 128, 1000, 2048, 4096, 100000):
-                fused = fused_decode_splits(batch, groups, ctx)
+                fused = fused_decode_splits(batch, groups, ctx, SMS)
                 assert fused in (1, 2, 4, 8)
                 assert fused * 128 <= max(ctx, 128)                       # at least 128 keys a piece
-                plain = decode_splits(batch, groups, ctx)
+                plain = decode_splits(batch, groups, ctx, SMS)
                 assert 1 <= plain <= 64 and plain * 128 <= max(ctx, 128)
-    assert fused_decode_splits(8, 4, 2048) == 4 and fused_decode_splits(8, 4, 4096) == 8
-    assert fused_decode_splits(64, 4, 2048) == 1 and fused_decode_splits(1, 4, 2048) == 8
+    assert fused_decode_splits(8, 4, 2048, SMS) == 4 and fused_decode_splits(8, 4, 4096, SMS) == 8
+    assert fused_decode_splits(64, 4, 2048, SMS) == 1 and fused_decode_splits(1, 4, 2048, SMS) == 8
+    assert fused_decode_splits(8, 4, 2048, 32) == 2               # a smaller GPU cuts contexts into fewer pieces
 
 
 def test_only_few_long_sequences_leave_the_cluster_kernel():
     def leaves(batch, groups, ctx, per_sm=2):
-        return wants_more_pieces(batch, groups, ctx, fused_decode_splits(batch, groups, ctx, per_sm=per_sm))
+        return wants_more_pieces(batch, groups, ctx, fused_decode_splits(batch, groups, ctx, SMS, per_sm=per_sm), SMS)
     assert leaves(1, 4, 32768) and leaves(2, 4, 32768)
     assert not leaves(1, 4, 8192) and not leaves(8, 4, 2048) and not leaves(8, 4, 16384)
     assert not leaves(8, 32, 2048, per_sm=1)              # many heads fill the GPU with one piece each

@@ -89,25 +89,33 @@ def test_linear_store_and_add(dtype, M, N, K):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,F,K", [(1, 176, 64), (5, 104, 80), (8, 5632, 2048), (40, 256, 96), (130, 24, 72),
                                    (24, 72, 264), (64, 5632, 2048), (128, 200, 520)])
-def test_linear_gated(dtype, M, F, K):
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_linear_gated(dtype, M, F, K, activation):
+    """``act(gate) * up`` in the epilogue of one projection, for every activation the kernels name (the
+    Llama feed-forward uses silu; the other one shows that the parameter is carried by every kernel)."""
     from stratakv_b200 import ops
     k = lib(dtype)
     a = torch.randn(M, K, device="cuda").to(dtype)
     w = (torch.randn(2 * F, K, device="cuda") / math.sqrt(K)).to(dtype)      # gate rows, then up rows
     out = torch.full((M, F), float("nan"), device="cuda").to(dtype)
-    k.linear(a, pack_gate_up(w), out, ops.MODE_GATED, "silu")
+    k.linear(a, pack_gate_up(w), out, ops.MODE_GATED, activation)
     gate = a.double() @ w[:F].double().T
     up = a.double() @ w[F:].double().T
-    ref = gate * torch.sigmoid(gate) * up
-    if dtype == torch.float32:
-        # float accumulation errs by at most ~2e-6 (1 + sum |a||w|) in gate and in up
-        # (tests/gemv_smoke.cu:259-272); silu has slope <= 1.1
-        err_gate = 2e-6 * (1 + a.double().abs() @ w[:F].double().abs().T)
-        err_up = 2e-6 * (1 + a.double().abs() @ w[F:].double().abs().T)
-        allowed = 1.1 * err_gate * up.abs() + (gate * torch.sigmoid(gate)).abs() * err_up + 1e-6 * ref.abs() + 1e-9
-        assert ((out.double() - ref).abs() <= allowed).all()
-    else:
-        close(out, ref, dtype)
+    act = gated_activation(gate, activation)
+    ref = act * up
+    # float accumulation errs by at most ~2e-6 (1 + sum |a||w|) in gate and in up
+    # (tests/gemv_smoke.cu:259-272); both activations have slopes below 1.2
+    err_gate = 2e-6 * (1 + a.double().abs() @ w[:F].double().abs().T)
+    err_up = 2e-6 * (1 + a.double().abs() @ w[F:].double().abs().T)
+    rounding = 1e-6 if dtype == torch.float32 else 2.0 ** -8
+    allowed = 1.2 * err_gate * up.abs() + act.abs() * err_up + rounding * ref.abs() + 1e-9
+    assert ((out.double() - ref).abs() <= allowed).all()
+
+
+def gated_activation(gate, name):
+    if name == "silu":
+        return gate * torch.sigmoid(gate)
+    return torch.nn.functional.gelu(gate, approximate="tanh")
 
 
 def _products(a, w, chunk=512):
@@ -163,12 +171,13 @@ def test_linear_tiled_tensor_memory_kernel_at_model_sizes(M, N, K, modes):
         else:
             F = N // 2
             out = torch.full((M, F), float("nan"), device="cuda").to(dtype)
-            k.linear(a, pack_gate_up(w), out, ops.MODE_GATED, "silu")
             gate, up = ref[:, :F], ref[:, F:]
-            want = gate * torch.sigmoid(gate) * up
-            slack = (1.1 * allowed[:, :F] * up.abs() + (gate * torch.sigmoid(gate)).abs() * allowed[:, F:]
-                     + 2.0 ** -8 * want.abs() + 1e-9)
-            assert ((out.double() - want).abs() <= slack).all(), mode
+            for activation in ("silu", "gelu_tanh"):
+                k.linear(a, pack_gate_up(w), out, ops.MODE_GATED, activation)
+                act = gated_activation(gate, activation)
+                want = act * up
+                slack = 1.2 * allowed[:, :F] * up.abs() + act.abs() * allowed[:, F:] + 2.0 ** -8 * want.abs() + 1e-9
+                assert ((out.double() - want).abs() <= slack).all(), (mode, activation)
         torch.cuda.synchronize()
         assert int(k.error_flag.item()) == 0
 
