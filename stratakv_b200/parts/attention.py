@@ -91,14 +91,23 @@ class PagedAttention(Mixer):
         self.w_o = self.rt.upload(tensors[s.o_weight])
 
     def forward(self, step, h, x, cache_entry, writes_cache=True):
-        s, rt = self.spec, self.rt
-        ops = rt.kernels(s.head_dim)
+        rt = self.rt
+        ops = rt.kernels(self.spec.head_dim)
         n = h.shape[0]
         qkv = rt.workspace.get("qkv", (n, self.q_dim + 2 * self.kv_dim), torch.float32)
         ops.linear(h, self.w_qkv, qkv, _ops.MODE_STORE_F32)
+        ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
+        self.attend(step, qkv, ctx, cache_entry, writes_cache)
+        ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
+
+    def attend(self, step, qkv, ctx, cache_entry, writes_cache=True):
+        """From the float32 q|k|v rows of the step's tokens to the attention output ``ctx`` (compute dtype):
+        position encoding, cache write, attention over each sequence's own keys."""
+        s, rt = self.spec, self.rt
+        ops = rt.kernels(s.head_dim)
+        n = qkv.shape[0]
         k_cache, v_cache = step.cache.entry_kv(cache_entry)
         table = step.block_tables[step.cache.entry_group_index(cache_entry)]
-        ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
         blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
         fused = (step.is_decode and rt.dtype == torch.bfloat16 and hasattr(self.position, "fusion_table")
                  and ops.has_attention_decode_fused())
@@ -110,7 +119,6 @@ class PagedAttention(Mixer):
             ops.attention_decode_fused(qkv, self.position.fusion_table(step.max_ctx), k_cache, v_cache, table,
                                        step.ctx_after, ctx, s.num_heads, s.num_kv_heads, s.head_dim,
                                        step.cache.block_size, s.scale, s.window, splits, writes_cache)
-            ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
             return
         q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
         self.position.rotate_and_store(step, qkv, q, k_cache, v_cache, table, s.num_heads, s.num_kv_heads,
@@ -134,7 +142,6 @@ class PagedAttention(Mixer):
         else:
             ops.attention(q, k_cache, v_cache, table, step.positions, step.token_seq, ctx, s.num_heads,
                           s.num_kv_heads, s.head_dim, step.cache.block_size, s.scale, s.window)
-        ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
 
 
 register_mixer("attention", PagedAttention)
