@@ -47,6 +47,13 @@ LLAMA3_8B = dict(TINYLLAMA, hidden_size=4096, intermediate_size=14336, num_hidde
                  num_key_value_heads=8, head_dim=128, vocab_size=128256, rope_theta=500000.0,
                  max_position_embeddings=8192)
 SHAPES = {"tinyllama-1.1b": TINYLLAMA, "llama2-7b": LLAMA2_7B, "llama3-8b": LLAMA3_8B}
+# Generation workloads of the larger shapes: requests that start together with prompt lengths drawn uniformly
+# (seeded) from a range, a number of new tokens each, greedy or sampled.
+WORKLOADS = {
+    "llama2-7b": dict(shape="llama2-7b", batch=8, prompt_range=(256, 2048), new_tokens=256, temperature=0.0),
+    "llama3-8b": dict(shape="llama3-8b", batch=64, prompt_range=(128, 1024), new_tokens=128, temperature=0.8),
+    "tinyllama-1.1b": dict(shape="tinyllama-1.1b", batch=8, prompt_range=(256, 2048), new_tokens=256, temperature=0.0),
+}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -117,7 +124,7 @@ def make_engine(layers: int, max_tokens: int, max_batch: int, shape=None):
     from stratakv_b200 import Engine, EngineConfig, LlamaConfig
     raw = dict(shape or TINYLLAMA, num_hidden_layers=layers)
     config = LlamaConfig.from_dict(raw)
-    engine_config = EngineConfig(max_tokens=max_tokens, dtype="bfloat16", max_batch=max_batch)
+    engine_config = EngineConfig(max_tokens=max_tokens, dtype="bfloat16", max_batch=max_batch, max_context=max_tokens)
     from stratakv_b200.config.registry import resolve_architecture
     from stratakv_b200.engine.model import expected_tensors
     from stratakv_b200.weights import random_tensors
@@ -341,6 +348,79 @@ def reference_arm(args) -> int:
     return 0
 
 
+def workload_arm(args) -> int:
+    """A whole workload through the Python entry point: ``Engine.generate`` on host token ids, every chosen token
+    read back to the host each step.  Reports decode tokens a second, the time of a decode step, the prompt step's
+    tokens a second, and the decode step against HBM from the bytes that are live (every weight once per step, and the
+    cache of the sequences at their mean length)."""
+    import random
+    import torch
+    from stratakv_b200.sampling import SamplingParams
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    work = WORKLOADS[args.workload]
+    shape = SHAPES[work["shape"]]
+    layers = args.layers or shape["num_hidden_layers"]
+    batch, new_tokens = work["batch"], work["new_tokens"]
+    rng = random.Random(0)
+    lengths = [rng.randint(*work["prompt_range"]) for _ in range(batch)]
+    prompts = [random_ids(length, shape["vocab_size"], 5000 + i) for i, length in enumerate(lengths)]
+    max_tokens = sum(-(-(length + new_tokens) // 64) * 64 for length in lengths) + 64
+    engine, config = make_engine(layers, max_tokens, batch, shape)
+    params = SamplingParams(temperature=work["temperature"], seed=1)
+    # warm-up: the same requests once (kernels loaded, buffers sized, decode graphs of every table width captured)
+    engine.generate(prompts, new_tokens, params, ignore_eos=True)
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    sampler.start()
+    output = engine.generate(prompts, new_tokens, params, ignore_eos=True)
+    clocks = sampler.stop()
+    t = output.timings
+    steps = new_tokens - 1                                   # the last chosen token is not fed
+    ms_per_step = t.decode_ms / steps
+    peak = peaks()
+    weight_bytes = engine.model.weight_bytes()
+    mean_context = sum(lengths) / batch + new_tokens / 2
+    kv_bytes = batch * mean_context * engine.cache.bytes_per_token()
+    achieved = (weight_bytes + kv_bytes) / (ms_per_step * 1e-3) / 1e9
+    io_bytes = engine.last_step_io_bytes()
+    value = t.decode_tps
+    print(json.dumps({
+        "metric": f"decode tokens/s ({args.workload} workload through Engine.generate, bf16, batch {batch})",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": steps, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random N(0,0.02) weights, uniform random token ids, seeded prompt lengths",
+        "config": {"model": f"{work['shape']} shape", "layers": layers, "layers_of_model": shape["num_hidden_layers"],
+                   "hidden": config.hidden_size, "heads": config.num_attention_heads,
+                   "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim, "ffn": config.intermediate_size,
+                   "vocab": config.vocab_size, "global_batch": batch, "prompt_min": work["prompt_range"][0],
+                   "prompt_max": work["prompt_range"][1], "prompt_tokens": sum(lengths), "new_tokens": new_tokens,
+                   "temperature": work["temperature"], "parallelism": "single GPU",
+                   "l2": f"inputs larger than L2 (weights {weight_bytes / 1e9:.1f} GB per step)"},
+        "clocks": clocks,
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": io_bytes[0], "d2h_bytes_per_step": io_bytes[1],
+                "prefill_ms": t.prefill_ms},
+        "prefill": {"value": t.prefill_tokens * 1000.0 / t.prefill_ms, "tokens": t.prefill_tokens, "ms": t.prefill_ms,
+                    "frac": prefill_flops_of(config, lengths) / (t.prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12),
+                    "of": peak["source"]},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peak["hbm_gbs"], "of": peak["source"], "weight_bytes": weight_bytes,
+                     "kv_bytes": int(kv_bytes)},
+        "gpu_launches": engine.launch_count(), "impl": "ours"}))
+    return 0
+
+
+def prefill_flops_of(config, lengths):
+    """FLOPs of one step that runs prompts of these lengths (the head runs on one row per prompt)."""
+    per_token = 2 * (config.hidden_size * (config.q_dim + 2 * config.kv_dim) + config.q_dim * config.hidden_size
+                     + 3 * config.hidden_size * config.intermediate_size)
+    linear = config.num_hidden_layers * per_token * sum(lengths) + 2 * config.hidden_size * config.vocab_size * len(lengths)
+    attention = sum(config.num_hidden_layers * 4 * config.num_attention_heads * config.head_dim * n * (n + 1) // 2
+                    for n in lengths)
+    return linear + attention
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -351,12 +431,17 @@ def main() -> int:
     parser.add_argument("--shape", default="tinyllama-1.1b", choices=sorted(SHAPES))
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
+    parser.add_argument("--context", type=int, default=CONTEXT, help="context at which the timed decode steps end")
+    parser.add_argument("--workload", choices=sorted(WORKLOADS),
+                        help="a whole generation workload through Engine.generate instead of the step benchmark")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload:
+        return workload_arm(args)
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
 
@@ -368,12 +453,13 @@ def main() -> int:
     if args.layers is None:
         args.layers = shape["num_hidden_layers"]
     vocab = shape["vocab_size"]
-    start_context = CONTEXT - steps - warmup                 # the timed steps end at the named context
+    context = args.context
+    start_context = context - steps - warmup                 # the timed steps end at the named context
     if start_context < 1:
-        print("bench.py: --steps plus --warmup must stay below the context of 2048")
+        print(f"bench.py: --steps plus --warmup must stay below the context of {context}")
         return 1
     biggest = 64 if not args.skip_points else args.batch
-    max_tokens = max(biggest * (CONTEXT + 64), PREFILL_TOKENS + 64)
+    max_tokens = max(biggest * (context + 64), PREFILL_TOKENS + 64)
     engine, config = make_engine(args.layers, max_tokens, max(biggest, args.batch), shape)
     peak = peaks()
 
@@ -396,7 +482,7 @@ def main() -> int:
                 "kv_bytes": int(kv_bytes)}
 
     result = {
-        "metric": f"decode tokens/s ({args.shape} shape, bf16, batch {args.batch}, context {CONTEXT})",
+        "metric": f"decode tokens/s ({args.shape} shape, bf16, batch {args.batch}, context {context})",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
@@ -404,7 +490,7 @@ def main() -> int:
                    "hidden": config.hidden_size, "heads": config.num_attention_heads,
                    "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
                    "ffn": config.intermediate_size, "vocab": config.vocab_size, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "context_at_end": final_context, "parallelism": "single GPU",
+                   "seq_len": context, "context_at_end": final_context, "parallelism": "single GPU",
                    "cache_block": engine.cache.block_size, "l2": f"inputs larger than L2 (weights {engine.model.weight_bytes() / 1e9:.1f} GB per step)"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "impl": "ours",
     }

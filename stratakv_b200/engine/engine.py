@@ -304,15 +304,24 @@ class Engine:
             stop_ids = self.spec.stop_token_ids
 
         on_gpu = self.device.type == "cuda"
-        landing = torch.empty(max(1, len(prompts)), dtype=torch.int32, pin_memory=on_gpu)   # chosen ids arrive here
+        rows = max(1, len(prompts))
+        landing = torch.empty(rows, dtype=torch.int32, pin_memory=on_gpu)   # chosen ids arrive here
         landed = torch.cuda.Event() if on_gpu else None
+        # streams and counters of a sampled step leave from pinned memory in one copy; the array may be
+        # rewritten once the step's tokens have landed, which the loop waits for anyway
+        draw_host = torch.empty((2, rows), dtype=torch.int32, pin_memory=on_gpu)
+        draw_device = torch.empty((2, rows), dtype=torch.int32, device=self.device)
+        draw_np = draw_host.numpy()
 
         def choose(logits, row_streams, counters):
             if params.greedy:
                 tokens = sampler.sample(logits, None, None)
             else:
-                meta = torch.tensor([row_streams, counters], dtype=torch.int32).to(self.device)
-                tokens = sampler.sample(logits, meta[0], meta[1])
+                count = len(row_streams)
+                draw_np[0, :count] = row_streams
+                draw_np[1, :count] = counters
+                draw_device.copy_(draw_host, non_blocking=True)
+                tokens = sampler.sample(logits, draw_device[0, :count], draw_device[1, :count])
             count = tokens.numel()
             self._io_bytes = (self._io_bytes[0], count * 4)
             if not on_gpu:
