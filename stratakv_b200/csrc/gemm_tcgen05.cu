@@ -291,6 +291,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
                     int N, int K, int mode, int act, int* __restrict__ flag) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    // tensor memory is handed out in powers of two columns: two accumulators, each at the start of a half
+    constexpr uint32_t TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512), ACC_STRIDE = TMEM_COLS / 2;
+    static_assert(BN % 32 == 0 && BN <= 256 && STAGE_BYTES % 1024 == 0, "tile width");
     constexpr uint32_t SLAB_BYTES = 4 * 2 * 4096;           // four epilogue warps, two 32 x 128-byte slabs each
     extern __shared__ uint8_t smem_raw[];
     // tiles and slabs need 1024-byte alignment for the 128-byte swizzle
@@ -314,7 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         // two accumulators of BN columns each: the epilogue of one tile overlaps the main loop of the next
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_addr(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+                     ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -357,7 +360,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
-            const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+            const uint32_t acc = tmem_base + (uint32_t)buf * ACC_STRIDE;
             for (int i = 0; i < k_iters; ++i, ++it) {
                 const int s = it % STAGES;
                 ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, flag);
@@ -386,7 +389,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
-            epilogue_tile<BN>(tmem_base + (uint32_t)(buf * BN), quarter, lane, slabs, buffer, &map_out, tma_out, out, M, N,
+            epilogue_tile<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, tma_out, out, M, N,
                               mode, act, m0, n0);
             // the accumulator has been read out: hand it back to the issuer
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -402,7 +405,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -658,6 +661,8 @@ static int tensor_map(const void* base, int rows, int cols, int elem_bytes, int 
     return 0;
 }
 
+static int tc_sm_count() { return sm_count(); }
+
 template <int BN, int STAGES>
 static int launch_tc(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
                      cudaStream_t stream) {
@@ -752,9 +757,23 @@ int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K,
     if (M <= 32) return launch_few_tokens<32, 8>(a, w, out, M, N, K, mode, act, flag, stream);
     if (M <= 64) return launch_few_tokens<64, 8>(a, w, out, M, N, K, mode, act, flag, stream);
     if (M <= 128) return launch_few_tokens<128, 6>(a, w, out, M, N, K, mode, act, flag, stream);
-    // Wider tiles re-read less of A and W from L2 per flop; narrow ones waste less on small N.
-    if (N > 128 && (long long)((M + 127) / 128) * ((N + 255) / 256) >= 96)
-        return launch_tc<256, 4>(a, w, out, M, N, K, mode, act, flag, stream);
+    // Wider tiles re-read less of A and W from L2 per flop (measured at 2,048 x 6,144 x 4,096: 1,268 TFLOP/s with
+    // 256-wide tiles, 1,014 with 160, 860 with 128); narrow ones waste less on small N and fill the last round of
+    // tiles better: 2,048 tokens x 2,560 columns are 160 tiles of 256 columns (two rounds on 148 SMs, the second nearly
+    // empty: 27.9 us) but 256 tiles of 160 (two rounds of five eighths the work: 25.6 us).  Cost of a width: rounds x
+    // width / efficiency per flop.  A width of 160
+    // serves the float epilogues only (its slabs of 32 columns divide it; the 64- and 128-column slabs of the
+    // other two modes do not).
+    const long long m_tiles = (M + 127) / 128;
+    auto cost = [&](int width, double efficiency) {
+        const long long tiles = m_tiles * ((N + width - 1) / width);
+        return (double)((tiles + tc_sm_count() - 1) / tc_sm_count()) * width / efficiency;
+    };
+    const bool float_out = mode == TC_MODE_STORE_F32 || mode == TC_MODE_ADD_F32;
+    const double wide = N > 128 ? cost(256, 1.0) : 1e30, narrow = cost(128, 0.68);
+    const double middle = (float_out && N > 128) ? cost(160, 0.80) : 1e30;
+    if (middle < wide && middle < narrow) return launch_tc<160, 5>(a, w, out, M, N, K, mode, act, flag, stream);
+    if (wide <= narrow) return launch_tc<256, 4>(a, w, out, M, N, K, mode, act, flag, stream);
     return launch_tc<128, 4>(a, w, out, M, N, K, mode, act, flag, stream);
 }
 

@@ -142,6 +142,8 @@ def _products(a, w, chunk=512):
     (300, 32001, 2048, "store_f32 store add"),       # rows of an odd width: stored by the threads
     (2048, 32001, 2048, "store_f32"),
     (1000, 4112, 1032, "store_f32 store add gated"),  # tails in M, N and K at once
+    (2048, 2500, 2048, "store_f32 add"),             # 160-wide tiles (256 of them, five stages), the last one clipped
+    (1500, 2501, 520, "store_f32 store add"),        # 160-wide tiles whose rows the threads store themselves
 ])
 def test_linear_tiled_tensor_memory_kernel_at_model_sizes(M, N, K, modes):
     """tests/gemv_smoke.cu:329-357 takes the reference's kernels to the model's shapes with a bound from
