@@ -133,17 +133,23 @@ class DecodeGraph:
         """True if ``stage_rows`` has prepared exactly this step (these sequences at these lengths)."""
         return self.staged is not None and self.staged == self._key(slots, ctx_before)
 
-    def fill(self, slots: Sequence[int], tokens: Sequence[int], ctx_before: Sequence[int], staged: bool = False) -> None:
-        """``staged``: the caller has checked ``staged_for`` for this step."""
+    def fill(self, slots: Sequence[int], tokens, ctx_before: Sequence[int], staged: bool = False,
+             device_tokens=None) -> None:
+        """``staged``: the caller has checked ``staged_for`` for this step.  ``tokens``: the token ids on the host,
+        or None with ``device_tokens`` (int32 on the device, the slots' order): they are copied into place on the
+        device, behind the copy of everything else."""
         if not staged:
             self.stage_rows(slots, ctx_before)
         self.staged = None
         live = len(slots)
         ids = self._np("token_ids")
-        ids[:live] = tokens
+        if tokens is not None:
+            ids[:live] = tokens
         if live < self.bucket:
             ids[live:] = 0
         self.device.copy_(self.host, non_blocking=True)
+        if tokens is None:
+            self._dev("token_ids")[:live].copy_(device_tokens[:live], non_blocking=True)
         self.copied.record()
         self.copy_pending = True
 

@@ -212,18 +212,8 @@ class Engine:
 
     def _decode_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """One token per sequence: the step runs as a CUDA graph of its batch-size bucket."""
-        from .decode_graph import DecodeGraph, bucket_for
         vocab = self.spec.vocab_size
         slots = [e.slot for e in entries]
-        if len(set(slots)) != len(slots):
-            raise StepError("a sequence appears twice in one step")
-        if len(entries) > self.config.slots:
-            raise StepError(f"{len(entries)} sequences in one step; the engine holds {self.config.slots}")
-        sequences = self.cache.sequences
-        try:
-            ctx_before = [sequences[slot].length for slot in slots]
-        except KeyError as missing:
-            raise StepError(f"slot {missing.args[0]} is not open") from None
         tokens = [int(e.tokens[0]) for e in entries]
         if min(tokens) < 0 or max(tokens) >= vocab:
             slot, token = next((s, t) for s, t in zip(slots, tokens) if not (0 <= t < vocab))
@@ -234,11 +224,41 @@ class Engine:
                 if int(w) != 0:
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside this step's 1 tokens")
                 rows.append(index)
+        logits = self._launch_decode(slots, tokens, None)
+        if not rows:
+            return None
+        if len(rows) == len(entries):
+            return logits[:len(entries)]
+        return logits[torch.tensor(rows, device=self.device)]
+
+    def step_ahead(self, slots: Sequence[int], device_tokens: torch.Tensor) -> torch.Tensor:
+        """A decode step whose token ids are already on the device (int32, one per slot, in the slots' order), for
+        a caller that launches a step before the host has read the tokens the step before chose.  Returns the
+        logits of every sequence.  Only engines that run decode steps as graphs have it (``can_step_ahead``)."""
+        if device_tokens.dtype != torch.int32 or device_tokens.numel() < len(slots):
+            raise StepError("step_ahead: one int32 token id per slot is needed")
+        return self._launch_decode(list(slots), None, device_tokens)[:len(slots)]
+
+    @property
+    def can_step_ahead(self) -> bool:
+        return bool(self._use_graphs)
+
+    def _launch_decode(self, slots, tokens, device_tokens) -> torch.Tensor:
+        from .decode_graph import DecodeGraph, bucket_for
+        if len(set(slots)) != len(slots):
+            raise StepError("a sequence appears twice in one step")
+        if len(slots) > self.config.slots:
+            raise StepError(f"{len(slots)} sequences in one step; the engine holds {self.config.slots}")
+        sequences = self.cache.sequences
+        try:
+            ctx_before = [sequences[slot].length for slot in slots]
+        except KeyError as missing:
+            raise StepError(f"slot {missing.args[0]} is not open") from None
         wanted = {slot: before + 1 for slot, before in zip(slots, ctx_before)}
         if self.max_context and max(ctx_before) + 1 > self.max_context:
             for slot, length in wanted.items():
                 self._check_context(slot, length)
-        bucket = bucket_for(len(entries))
+        bucket = bucket_for(len(slots))
         graph = self._graphs.get(bucket)
         staged = graph is not None and graph.staged_for(slots, ctx_before)
         if not staged:                          # (a staged step needs no new block and fits its graph: see _stage_next)
@@ -250,17 +270,13 @@ class Engine:
                     width *= 2
                 graph = DecodeGraph(self, bucket, width)
                 self._graphs[bucket] = graph
-        graph.fill(slots, tokens, ctx_before, staged)
+        graph.fill(slots, tokens, ctx_before, staged, device_tokens)
         logits = graph.run()
         self._io_bytes = (graph.host.numel() * 4, self._io_bytes[1])
         for slot, length in wanted.items():
             self.cache.advance(slot, length)
         self._stage_next(graph, slots)
-        if not rows:
-            return None
-        if len(rows) == len(entries):
-            return logits[:len(entries)]
-        return logits[torch.tensor(rows, device=self.device)]
+        return logits
 
     def _stage_next(self, graph, slots) -> None:
         """While the step just launched runs: prepare the metadata of the step that most likely
@@ -303,36 +319,9 @@ class Engine:
         elif stop_ids is None:
             stop_ids = self.spec.stop_token_ids
 
-        on_gpu = self.device.type == "cuda"
-        rows = max(1, len(prompts))
-        landing = torch.empty(rows, dtype=torch.int32, pin_memory=on_gpu)   # chosen ids arrive here
-        landed = torch.cuda.Event() if on_gpu else None
-        # streams and counters of a sampled step leave from pinned memory in one copy; the array may be
-        # rewritten once the step's tokens have landed, which the loop waits for anyway
-        draw_host = torch.empty((2, rows), dtype=torch.int32, pin_memory=on_gpu)
-        draw_device = torch.empty((2, rows), dtype=torch.int32, device=self.device)
-        draw_np = draw_host.numpy()
-
-        def choose(logits, row_streams, counters):
-            if params.greedy:
-                tokens = sampler.sample(logits, None, None)
-            else:
-                count = len(row_streams)
-                draw_np[0, :count] = row_streams
-                draw_np[1, :count] = counters
-                draw_device.copy_(draw_host, non_blocking=True)
-                tokens = sampler.sample(logits, draw_device[0, :count], draw_device[1, :count])
-            count = tokens.numel()
-            self._io_bytes = (self._io_bytes[0], count * 4)
-            if not on_gpu:
-                return tokens.tolist()
-            landing[:count].copy_(tokens, non_blocking=True)
-            landed.record()
-            landed.synchronize()
-            return landing[:count].tolist()
-
+        chooser = _Chooser(self, sampler, params, max(1, len(prompts)))
         sync = torch.cuda.synchronize if self.device.type == "cuda" else (lambda: None)
-        output = run(self, choose, prompts, max_new_tokens, stop_ids, streams, sync=sync)
+        output = run(self, chooser, prompts, max_new_tokens, stop_ids, streams, sync=sync)
         self.check_flags()
         return output
 
@@ -349,6 +338,61 @@ class Engine:
         if flags:
             self.model.flags.zero_()
             raise StepError(f"device flags raised: {flags:#x} ({describe_flags(flags)})")
+
+
+class _Chooser:
+    """Chooses one token per row of a step's logits on the device and brings the ids to the host.
+
+    Called like a function it waits for the ids.  ``launch`` only queues the work and returns a handle;
+    ``tokens_device(handle)`` is where the ids will be on the device (a following step can be fed from there),
+    ``result(handle)`` waits and returns them.  Three sets of buffers rotate, so two choices may be in flight
+    while a third is read.  Streams and counters of a sampled step leave from pinned memory in one copy."""
+    RING = 3
+
+    def __init__(self, engine, sampler, params, rows: int):
+        self.engine, self.sampler, self.params = engine, sampler, params
+        self.on_gpu = engine.device.type == "cuda"
+        pin = self.on_gpu
+        self.chosen = [torch.empty(rows, dtype=torch.int32, device=engine.device) for _ in range(self.RING)]
+        self.landing = [torch.empty(rows, dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
+        self.landed = [torch.cuda.Event() if self.on_gpu else None for _ in range(self.RING)]
+        self.draw_host = [torch.empty((2, rows), dtype=torch.int32, pin_memory=pin) for _ in range(self.RING)]
+        self.draw_device = [torch.empty((2, rows), dtype=torch.int32, device=engine.device) for _ in range(self.RING)]
+        self.counts = [0] * self.RING
+        self.turn = 0
+
+    def launch(self, logits, row_streams, counters) -> int:
+        handle = self.turn
+        self.turn = (self.turn + 1) % self.RING
+        count = logits.shape[0]
+        out = self.chosen[handle][:count]
+        if self.params.greedy:
+            self.sampler.sample(logits, None, None, out)
+        else:
+            host = self.draw_host[handle].numpy()
+            host[0, :count] = row_streams
+            host[1, :count] = counters
+            self.draw_device[handle].copy_(self.draw_host[handle], non_blocking=True)
+            self.sampler.sample(logits, self.draw_device[handle][0, :count], self.draw_device[handle][1, :count], out)
+        self.counts[handle] = count
+        self.engine._io_bytes = (self.engine._io_bytes[0], count * 4)
+        if self.on_gpu:
+            self.landing[handle][:count].copy_(out, non_blocking=True)
+            self.landed[handle].record()
+        return handle
+
+    def tokens_device(self, handle: int) -> torch.Tensor:
+        return self.chosen[handle][:self.counts[handle]]
+
+    def result(self, handle: int):
+        count = self.counts[handle]
+        if not self.on_gpu:
+            return self.chosen[handle][:count].tolist()
+        self.landed[handle].synchronize()
+        return self.landing[handle][:count].tolist()
+
+    def __call__(self, logits, row_streams, counters):
+        return self.result(self.launch(logits, row_streams, counters))
 
 
 FLAG_MEANINGS = {1: "a token id outside the vocabulary reached the embedding",

@@ -125,6 +125,66 @@ def generate(engine, choose: Callable, prompts: Sequence[Sequence[int]], max_new
     return GenerationOutput(sequences, timings)
 
 
+def _take(engine, members, tokens, slots, sequences, prompts, budgets, stop):
+    """Append each member's new token; a member whose token is a stop token or whose budget is reached leaves the
+    batch at once (its slot and blocks go back).  Returns the members that go on."""
+    still = []
+    for i, token in zip(members, tokens):
+        sequences[i].append(int(token))
+        produced = len(sequences[i]) - len(prompts[i])
+        if int(token) in stop or produced >= budgets[i]:
+            engine.close_sequence(slots.pop(i))
+        else:
+            still.append(i)
+    return still
+
+
+def _decode_in_turn(engine, choose, live, chosen, slots, sequences, prompts, budgets, stop, streams, timings):
+    """Step, choose, read the tokens, step again: the host knows every token before it feeds it."""
+    while True:
+        live = _take(engine, live, chosen, slots, sequences, prompts, budgets, stop)
+        if not live:
+            return
+        logits = engine.step([StepEntry(slots[i], [sequences[i][-1]], [0]) for i in live])
+        chosen = choose(logits, [streams[i] for i in live], [len(sequences[i]) - len(prompts[i]) for i in live])
+        timings.decode_tokens += len(live)
+
+
+def _decode_ahead(engine, chooser, live, chosen, slots, sequences, prompts, budgets, stop, streams, timings):
+    """The same results with the host one step behind the device: while it reads the tokens that a step chose,
+    the next step, fed with those tokens where they lie on the device, is already running.  A step is launched
+    ahead only for the very members of the step before it and only if none of them can reach its budget with
+    the token still unread; a member that turns out to have hit a stop token has then run one step in vain
+    (its row is dropped, its slot was still its own), and the loop falls back in step with the host."""
+    produced = lambda i: len(sequences[i]) - len(prompts[i])
+    live = _take(engine, live, chosen, slots, sequences, prompts, budgets, stop)
+    flying = None                                        # (members, handle): a step in flight whose tokens are unread
+    while live or flying:
+        if flying is None:
+            logits = engine.step([StepEntry(slots[i], [sequences[i][-1]], [0]) for i in live])
+            flying = (list(live), chooser.launch(logits, [streams[i] for i in live], [produced(i) for i in live]))
+        members, handle = flying
+        following = None
+        if all(produced(i) + 1 < budgets[i] for i in members):
+            logits = engine.step_ahead([slots[i] for i in members], chooser.tokens_device(handle))
+            following = chooser.launch(logits, [streams[i] for i in members], [produced(i) + 1 for i in members])
+        tokens = chooser.result(handle)
+        timings.decode_tokens += len(members)
+        live = _take(engine, members, tokens, slots, sequences, prompts, budgets, stop)
+        if following is None:
+            flying = None
+        elif live == members:
+            flying = (members, following)
+        else:                                            # somebody stopped: the step ahead ran a row for it in vain
+            tokens = chooser.result(following)
+            going = set(live)
+            pairs = [(i, token) for i, token in zip(members, tokens) if i in going]
+            timings.decode_tokens += len(pairs)
+            live = _take(engine, [i for i, _ in pairs], [token for _, token in pairs], slots, sequences, prompts,
+                         budgets, stop)
+            flying = None
+
+
 def _run_batch(engine, choose, members, sequences, prompts, budgets, stop, streams, timings, clock, sync):
     slots = {}
     try:
@@ -139,22 +199,9 @@ def _run_batch(engine, choose, members, sequences, prompts, budgets, stop, strea
         timings.prefill_ms += 1000.0 * (clock() - start)
         timings.prefill_tokens += sum(len(prompts[i]) for i in live)
         start = clock()
-        while True:
-            still = []
-            for i, token in zip(live, chosen):
-                sequences[i].append(int(token))
-                produced = len(sequences[i]) - len(prompts[i])
-                if int(token) in stop or produced >= budgets[i]:
-                    engine.close_sequence(slots.pop(i))          # leaves the batch at once
-                else:
-                    still.append(i)
-            live = still
-            if not live:
-                break
-            logits = engine.step([StepEntry(slots[i], [sequences[i][-1]], [0]) for i in live])
-            chosen = choose(logits, [streams[i] for i in live],
-                            [len(sequences[i]) - len(prompts[i]) for i in live])
-            timings.decode_tokens += len(live)
+        ahead = hasattr(choose, "launch") and getattr(engine, "can_step_ahead", False)
+        (_decode_ahead if ahead else _decode_in_turn)(engine, choose, live, chosen, slots, sequences, prompts, budgets,
+                                                       stop, streams, timings)
         sync()
         timings.decode_ms += 1000.0 * (clock() - start)
     finally:

@@ -138,3 +138,55 @@ def test_a_request_beyond_the_context_limit_is_refused_before_anything_runs():
         generate(engine, choose, [[1, 2], [1] * 8], [3, 6])
     assert engine.steps[-1][0][1] != [1, 2] and engine.cache.all_free()      # the first request did not run either
     assert generate(engine, choose, [[1] * 40], 0).sequences == [[1] * 40]   # nothing to run, nothing to refuse
+
+
+class AheadEngine(ScriptedEngine):
+    """A scripted engine that can also take a step's tokens from where the chooser left them ("on the device"),
+    as the real engine does for a host that runs one step behind."""
+    can_step_ahead = True
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.ahead_steps = 0
+
+    def step_ahead(self, slots, device_tokens):
+        from stratakv_b200.engine.engine import StepEntry
+        self.ahead_steps += 1
+        return self.step([StepEntry(slot, [int(token)], [0]) for slot, token in zip(slots, device_tokens.tolist())])
+
+
+class LaggingChooser:
+    """Chooses at once but hands the ids out only through ``result``; counts what was asked for."""
+
+    def __init__(self):
+        self.pending, self.launched = {}, 0
+
+    def launch(self, logits, streams, counters):
+        self.launched += 1
+        self.pending[self.launched] = torch.argmax(logits, dim=-1).to(torch.int32)
+        return self.launched
+
+    def tokens_device(self, handle):
+        return self.pending[handle]
+
+    def result(self, handle):
+        return self.pending.pop(handle).tolist()
+
+    def __call__(self, logits, streams, counters):
+        return self.result(self.launch(logits, streams, counters))
+
+
+@pytest.mark.parametrize("budgets,stop_ids", [([6, 6, 6], []), ([4, 1, 9], []), ([9, 9, 9], [13]), ([5, 7, 2], [33, 22]),
+                                              ([1, 1, 1], []), ([12, 3, 12], [12, 35])])
+def test_a_host_one_step_behind_gives_the_same_sequences(budgets, stop_ids):
+    """The loop that launches a step before it has read the last one's tokens returns what the loop in turn
+    returns, for every mix of budgets and stop tokens, gives every slot back, and drops the rows that ran in vain."""
+    prompts = [[10, 11], [20], [30, 31, 32]]
+    in_turn = generate(ScriptedEngine(), choose, prompts, budgets, stop_ids=stop_ids).sequences
+    engine, chooser = AheadEngine(), LaggingChooser()
+    out = generate(engine, chooser, prompts, budgets, stop_ids=stop_ids)
+    assert out.sequences == in_turn
+    assert engine.cache.all_free() and not chooser.pending
+    assert out.timings.decode_tokens == sum(len(s) - len(p) - 1 for s, p in zip(in_turn, prompts))
+    if max(budgets) > 2:
+        assert engine.ahead_steps > 0
