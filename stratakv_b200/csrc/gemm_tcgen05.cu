@@ -27,7 +27,22 @@
 
 namespace skv {
 
-enum { TC_MODE_STORE = 0, TC_MODE_STORE_F32 = 1, TC_MODE_ADD_F32 = 2, TC_MODE_GATED = 3 };
+enum { TC_MODE_STORE = 0, TC_MODE_STORE_F32 = 1, TC_MODE_ADD_F32 = 2, TC_MODE_GATED = 3, TC_MODE_QKV_ROPE = 4 };
+
+// What the q|k|v projection's epilogue needs to finish the job of rope_kv_write_vec_kernel (elementwise.cu)
+// itself: the output columns are [query heads | key heads | value heads]; queries and keys are rotated in float
+// with the host-built table (pairs (d, d + head_dim / 2), src/layers/attention.cpp:96-135), rounded to bfloat16
+// once, queries go to `q_out` (through the copy engine), keys and values of token m to row positions[m] of
+// the cache block that the block table of sequence token_seq[m] names.
+struct RopeArgs {
+    const float2* cos_sin;             // [positions][head_dim / 2] (cos, sin), or null: no rotation
+    const int* positions;              // [M]
+    const int* token_seq;              // [M]
+    const int* block_table;            // [sequences][table_width]
+    __nv_bfloat16* k_cache;            // [blocks][kv_heads][block_size][head_dim]
+    __nv_bfloat16* v_cache;
+    int table_width, num_heads, num_kv_heads, head_dim, block_size, write_kv;
+};
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;                      // 64 bfloat16 = one 128-byte swizzle row
@@ -285,11 +300,117 @@ __device__ __forceinline__ void epilogue_tile(uint32_t acc_tmem, int quarter, in
     }
 }
 
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+    return *(const uint32_t*)&pair;
+}
+
+// The epilogue of one tile of the q|k|v projection with the rotary encoding and the cache write folded in
+// (TC_MODE_QKV_ROPE; head size 64 or 128, which divide the tile's width).  A thread owns a token (a row of the
+// accumulator); head by head it reads 32 pairs (d, d + half) at a time, rotates them and rounds them.  A query
+// head's row goes into the warp's swizzled slabs (64 columns each) and out through the copy engine; key and
+// value rows are few (the KV heads) and go straight to their cache rows in 16-byte pieces.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_rope(uint32_t acc_tmem, int quarter, int lane, uint8_t* slabs, int& buffer,
+                                                   const CUtensorMap* map_q, const RopeArgs& rope, int M, int N, int m0,
+                                                   int n0) {
+    const int m = m0 + quarter * 32 + lane;
+    const bool row_live = m < M;
+    const int hd = rope.head_dim, half = hd >> 1, n_slabs = hd >> 6;
+    const uint32_t lane_base = acc_tmem + ((uint32_t)(quarter * 32) << 16);
+    const int y = m0 + quarter * 32;
+    const int pos = row_live ? rope.positions[m] : 0;
+    size_t cache_row = 0;                          // element offset of this token's row in KV head 0 of its block
+    if (row_live && rope.write_kv) {
+        const int block = rope.block_table[(size_t)rope.token_seq[m] * rope.table_width + pos / rope.block_size];
+        cache_row = ((size_t)block * rope.num_kv_heads * rope.block_size + (pos % rope.block_size)) * hd;
+    }
+    const float4* angles = rope.cos_sin ? (const float4*)(rope.cos_sin + (size_t)pos * half) : nullptr;
+#pragma unroll 1
+    for (int col0 = 0; col0 < BN && n0 + col0 < N; col0 += hd) {
+        const int head = (n0 + col0) / hd;
+        const int kind = head < rope.num_heads ? 0 : (head < rope.num_heads + rope.num_kv_heads ? 1 : 2);
+        if (kind != 0 && !rope.write_kv) continue;                  // a layer that only reads a cache another one wrote
+        if (kind == 2) {
+            __nv_bfloat16* dst = rope.v_cache + cache_row + (size_t)(head - rope.num_heads - rope.num_kv_heads) * rope.block_size * hd;
+#pragma unroll 1
+            for (int c = 0; c < hd; c += 32) {
+                uint32_t v[32];
+                tmem_load_32(lane_base + (uint32_t)(col0 + c), v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row_live) {
+#pragma unroll
+                    for (int piece = 0; piece < 4; ++piece)
+                        *(uint4*)(dst + c + 8 * piece) = make_uint4(
+                            pack_bf16(__uint_as_float(v[8 * piece]), __uint_as_float(v[8 * piece + 1])),
+                            pack_bf16(__uint_as_float(v[8 * piece + 2]), __uint_as_float(v[8 * piece + 3])),
+                            pack_bf16(__uint_as_float(v[8 * piece + 4]), __uint_as_float(v[8 * piece + 5])),
+                            pack_bf16(__uint_as_float(v[8 * piece + 6]), __uint_as_float(v[8 * piece + 7])));
+                }
+            }
+            continue;
+        }
+        uint8_t* slab0 = slabs;                    // a query head's row: one slab (head size 64) or both (128)
+        if (kind == 0) {
+            if (n_slabs == 1) {                    // the two slabs alternate: one is written while the other is being read
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                slab0 = slabs + buffer * 4096;
+            } else {
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            }
+            __syncwarp();
+        }
+        __nv_bfloat16* key_dst = rope.k_cache + cache_row + (size_t)(head - rope.num_heads) * rope.block_size * hd;
+#pragma unroll 1
+        for (int c = 0; c < half; c += 32) {       // pairs c .. c + 31
+            uint32_t lo[32], hi[32];
+            tmem_load_32(lane_base + (uint32_t)(col0 + c), lo);
+            tmem_load_32(lane_base + (uint32_t)(col0 + half + c), hi);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int piece = 0; piece < 4; ++piece) {                // eight pairs: one 16-byte piece of each half
+                uint32_t first[4], second[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {                        // two pairs at a time
+                    float4 cs = make_float4(1.0f, 0.0f, 1.0f, 0.0f);  // (cos, sin) of pairs 2e and 2e + 1 of the piece
+                    if (angles) cs = angles[(c + 8 * piece + 2 * e) >> 1];
+                    const float a0 = __uint_as_float(lo[8 * piece + 2 * e]), a1 = __uint_as_float(lo[8 * piece + 2 * e + 1]);
+                    const float b0 = __uint_as_float(hi[8 * piece + 2 * e]), b1 = __uint_as_float(hi[8 * piece + 2 * e + 1]);
+                    first[e] = pack_bf16(a0 * cs.x - b0 * cs.y, a1 * cs.z - b1 * cs.w);      // as rotated() of elementwise.cu
+                    second[e] = pack_bf16(a0 * cs.y + b0 * cs.x, a1 * cs.w + b1 * cs.z);
+                }
+                const uint4 low = make_uint4(first[0], first[1], first[2], first[3]);
+                const uint4 high = make_uint4(second[0], second[1], second[2], second[3]);
+                const int d_low = c + 8 * piece, d_high = half + c + 8 * piece;      // element of the head's row
+                if (kind == 0) {
+                    slab_write(slab0 + (d_low >> 6) * 4096, lane, (d_low & 63) >> 3, low);
+                    slab_write(slab0 + (d_high >> 6) * 4096, lane, (d_high & 63) >> 3, high);
+                } else if (row_live) {
+                    *(uint4*)(key_dst + d_low) = low;
+                    *(uint4*)(key_dst + d_high) = high;
+                }
+            }
+        }
+        if (kind == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                if (y < M) {
+                    for (int sl = 0; sl < n_slabs; ++sl)
+                        tma_store_2d(map_q, head * hd + sl * 64, y, smem_addr(slab0 + sl * 4096));
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            if (n_slabs == 1) buffer ^= 1;
+        }
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
-                    int N, int K, int mode, int act, int* __restrict__ flag) {
+                    int N, int K, int mode, int act, int* __restrict__ flag, const RopeArgs rope) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     // tensor memory is handed out in powers of two columns: two accumulators, each at the start of a half
     constexpr uint32_t TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512), ACC_STRIDE = TMEM_COLS / 2;
@@ -389,8 +510,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
-            epilogue_tile<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, tma_out, out, M, N,
-                              mode, act, m0, n0);
+            if (mode == TC_MODE_QKV_ROPE) {
+                if constexpr (BN % 128 == 0)
+                    epilogue_tile_rope<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, rope,
+                                           M, N, m0, n0);
+            } else {
+                epilogue_tile<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, tma_out, out,
+                                  M, N, mode, act, m0, n0);
+            }
             // the accumulator has been read out: hand it back to the issuer
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -665,16 +792,18 @@ static int tc_sm_count() { return sm_count(); }
 
 template <int BN, int STAGES>
 static int launch_tc(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
     CUtensorMap map_a, map_w, map_out;
     if (int code = tensor_map(a, M, K, 2, TC_BM, TC_BK, &map_a)) return code;
     if (int code = tensor_map(w, N, K, 2, BN, TC_BK, &map_w)) return code;
     // The epilogue stores through the copy engine when the output's rows are 16-byte multiples;
     // otherwise (an odd vocabulary, say) the threads store their rows themselves.
     const bool float_out = mode == TC_MODE_STORE_F32 || mode == TC_MODE_ADD_F32;
-    const int out_cols = mode == TC_MODE_GATED ? N / 2 : N;
+    // (with the rotary epilogue `out` is the queries' tensor, [M, heads x head size] bfloat16)
+    const int out_cols = mode == TC_MODE_GATED ? N / 2 : (mode == TC_MODE_QKV_ROPE ? rope.num_heads * rope.head_dim : N);
     const int out_elem = float_out ? 4 : 2;
     int tma_out = ((size_t)out_cols * out_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
+    if (mode == TC_MODE_QKV_ROPE && !tma_out) return fail("skv_linear_qkv_rope", "the queries' rows must be 16-byte multiples");
     if (tma_out) {
         if (int code = tensor_map(out, M, out_cols, out_elem, 32, float_out ? 32 : 64, &map_out)) return code;
     } else {
@@ -699,7 +828,7 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
     dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));     // one persistent block per SM at most
     return launch_pdl("skv_linear(tcgen05)", gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(TC_THREADS), smem, stream,
-                      map_a, map_w, map_out, tma_out, out, M, N, K, mode, act, flag);
+                      map_a, map_w, map_out, tma_out, out, M, N, K, mode, act, flag, rope);
 }
 
 template <int MP, int STAGES>
@@ -777,6 +906,64 @@ int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K,
     return launch_tc<128, 4>(a, w, out, M, N, K, mode, act, flag, stream);
 }
 
+// The q|k|v projection of a step with many tokens, with the rotary encoding and the cache write in its epilogue.
+int linear_tcgen05_qkv_rope(const void* a, const void* w, void* q_out, int M, int N, int K, const RopeArgs& rope,
+                            int* flag, cudaStream_t stream) {
+    if (K % 8 != 0) return fail("skv_linear_qkv_rope", "the inner size must be a multiple of 8 (16-byte rows)");
+    if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)q_out | (uintptr_t)rope.k_cache | (uintptr_t)rope.v_cache |
+         (uintptr_t)rope.cos_sin) & 15)
+        return fail("skv_linear_qkv_rope", "operands must be 16-byte aligned");
+    if (M <= 128) return fail("skv_linear_qkv_rope", "this form serves steps of more than 128 tokens");
+    if (rope.head_dim != 64 && rope.head_dim != 128) return fail("skv_linear_qkv_rope", "head size 64 or 128 only");
+    if (rope.num_heads <= 0 || rope.num_kv_heads <= 0 || N != (rope.num_heads + 2 * rope.num_kv_heads) * rope.head_dim)
+        return fail("skv_linear_qkv_rope", "the weight's rows must be [query heads | key heads | value heads]");
+    if (rope.block_size <= 0 || rope.table_width <= 0) return fail("skv_linear_qkv_rope", "bad cache block size or table width");
+    const long long m_tiles = (M + 127) / 128;
+    auto cost = [&](int width, double efficiency) {
+        const long long tiles = m_tiles * ((N + width - 1) / width);
+        return (double)((tiles + tc_sm_count() - 1) / tc_sm_count()) * width / efficiency;
+    };
+    if (cost(256, 1.0) <= cost(128, 0.68))
+        return launch_tc<256, 4>(a, w, q_out, M, N, K, TC_MODE_QKV_ROPE, 0, flag, stream, rope);
+    return launch_tc<128, 4>(a, w, q_out, M, N, K, TC_MODE_QKV_ROPE, 0, flag, stream, rope);
+}
+
 }  // namespace skv
+
+using namespace skv;
+
+SKV_EXPORT int skv_has_linear_qkv_rope() { return 1; }
+
+// out q [M, heads x head_dim] bfloat16 = rotated (a[M, K] . w[N, K]^T)[:, query columns]; keys (rotated) and values
+// of token m go to the cache row of position positions[m] of sequence token_seq[m] if write_kv.  See RopeArgs.
+SKV_EXPORT int skv_linear_qkv_rope(const void* a, const void* w, void* q_out, int M, int N, int K, const float* cos_sin,
+                                   const int* positions, const int* token_seq, const int* block_table, int table_width,
+                                   void* k_cache, void* v_cache, int num_heads, int num_kv_heads, int head_dim,
+                                   int block_size, int write_kv, int* flag, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    RopeArgs rope;
+    rope.cos_sin = (const float2*)cos_sin;
+    rope.positions = positions;
+    rope.token_seq = token_seq;
+    rope.block_table = block_table;
+    rope.k_cache = (__nv_bfloat16*)k_cache;
+    rope.v_cache = (__nv_bfloat16*)v_cache;
+    rope.table_width = table_width;
+    rope.num_heads = num_heads;
+    rope.num_kv_heads = num_kv_heads;
+    rope.head_dim = head_dim;
+    rope.block_size = block_size;
+    rope.write_kv = write_kv;
+    return linear_tcgen05_qkv_rope(a, w, q_out, M, N, K, rope, flag, stream);
+}
+
+#else
+
+SKV_EXPORT int skv_has_linear_qkv_rope() { return 0; }
+
+SKV_EXPORT int skv_linear_qkv_rope(const void*, const void*, void*, int, int, int, const float*, const int*, const int*,
+                                   const int*, int, void*, void*, int, int, int, int, int, int*, cudaStream_t) {
+    return skv::fail("skv_linear_qkv_rope", "only the bfloat16 build has this kernel");
+}
 
 #endif

@@ -196,6 +196,33 @@ class Kernels:
             else:
                 stats.invalidate()
 
+    def has_linear_qkv_rope(self) -> bool:
+        return bool(self.lib.skv_has_linear_qkv_rope())
+
+    def linear_qkv_rope(self, a, w, q_out, cos_sin, positions, token_seq, block_table, k_cache, v_cache,
+                        num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, write_kv: bool, flag=None):
+        """The q|k|v projection of a step of more than 128 tokens with ``rope_kv_write`` in its epilogue (bfloat16,
+        head size 64 or 128): ``q_out`` [M, heads * head_dim] gets the rotated queries, the cache the rotated keys and
+        the values of every token, at the row of its position in the block its sequence's table names."""
+        self._want(a, self.dtype, "a"); self._want(w, self.dtype, "w"); self._want(q_out, self.dtype, "q_out")
+        self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
+        self._want(block_table, torch.int32, "block_table")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
+        if cos_sin is not None:
+            self._want(cos_sin, torch.float32, "cos_sin")
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or N != (num_heads + 2 * num_kv_heads) * head_dim:
+            raise KernelError("linear_qkv_rope: the weight must be [(heads + 2 kv heads) * head_dim, K]")
+        if tuple(q_out.shape) != (M, num_heads * head_dim) or positions.numel() != M or token_seq.numel() != M:
+            raise KernelError("linear_qkv_rope: one query row, one position and one sequence index per token is needed")
+        if tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, head_dim) or k_cache.shape != v_cache.shape:
+            raise KernelError("linear_qkv_rope: the cache must be [blocks, kv_heads, block_size, head_dim]")
+        self._check(self.lib.skv_linear_qkv_rope(
+            _ptr(a), _ptr(w), _ptr(q_out), M, N, K, _ptr(cos_sin), _ptr(positions), _ptr(token_seq), _ptr(block_table),
+            block_table.shape[1], _ptr(k_cache), _ptr(v_cache), num_heads, num_kv_heads, head_dim, block_size,
+            int(bool(write_kv)), _ptr(flag if flag is not None else self.error_flag), _stream()), "linear_qkv_rope")
+
     def rope_kv_write(self, qkv, cos_sin, positions, token_seq, block_table, q_out, k_cache, v_cache,
                       num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, write_kv: bool):
         self._want(qkv, torch.float32, "qkv"); self._want(q_out, self.dtype, "q_out")

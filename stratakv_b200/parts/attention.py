@@ -91,13 +91,24 @@ class PagedAttention(Mixer):
         self.w_o = self.rt.upload(tensors[s.o_weight])
 
     def forward(self, step, h, x, cache_entry, writes_cache=True):
-        rt = self.rt
-        ops = rt.kernels(self.spec.head_dim)
+        s, rt = self.spec, self.rt
+        ops = rt.kernels(s.head_dim)
         n = h.shape[0]
-        qkv = rt.workspace.get("qkv", (n, self.q_dim + 2 * self.kv_dim), torch.float32)
-        ops.linear(h, self.w_qkv, qkv, _ops.MODE_STORE_F32)
         ctx = rt.workspace.get("attn_ctx", (n, self.q_dim), rt.dtype)
-        self.attend(step, qkv, ctx, cache_entry, writes_cache)
+        if (rt.dtype == torch.bfloat16 and n > 128 and s.head_dim in (64, 128) and torch.is_tensor(h)
+                and hasattr(self.position, "fusion_table") and ops.has_linear_qkv_rope()):
+            # many tokens: the projection's epilogue rotates queries and keys and writes the cache itself
+            q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
+            k_cache, v_cache = step.cache.entry_kv(cache_entry)
+            table = step.block_tables[step.cache.entry_group_index(cache_entry)]
+            ops.linear_qkv_rope(h, self.w_qkv, q, self.position.fusion_table(step.max_ctx), step.positions,
+                                step.token_seq, table, k_cache, v_cache, s.num_heads, s.num_kv_heads, s.head_dim,
+                                step.cache.block_size, writes_cache)
+            self._attend_rotated(step, q, ctx, k_cache, v_cache, table)
+        else:
+            qkv = rt.workspace.get("qkv", (n, self.q_dim + 2 * self.kv_dim), torch.float32)
+            ops.linear(h, self.w_qkv, qkv, _ops.MODE_STORE_F32)
+            self.attend(step, qkv, ctx, cache_entry, writes_cache)
         ops.linear(ctx, self.w_o, x, _ops.MODE_ADD_F32, stats=step.residual_stats)
 
     def attend(self, step, qkv, ctx, cache_entry, writes_cache=True):
@@ -123,6 +134,14 @@ class PagedAttention(Mixer):
         q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
         self.position.rotate_and_store(step, qkv, q, k_cache, v_cache, table, s.num_heads, s.num_kv_heads,
                                        s.head_dim, step.cache.block_size, writes_cache)
+        self._attend_rotated(step, q, ctx, k_cache, v_cache, table)
+
+    def _attend_rotated(self, step, q, ctx, k_cache, v_cache, table):
+        """Attention of the step's rotated queries ``q`` over the cache, which holds the step's keys and values."""
+        s, rt = self.spec, self.rt
+        ops = rt.kernels(s.head_dim)
+        n = q.shape[0]
+        blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
         if step.is_decode and rt.dtype == torch.bfloat16:
             splits = decode_splits(n, blocks_per_seq, step.max_ctx, rt.sm_count)
             scratch_o = scratch_ml = None

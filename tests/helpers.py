@@ -58,12 +58,15 @@ def random_tokens(vocab, length, seed):
     return torch.randint(0, vocab, (length,), generator=generator).tolist()
 
 
-def run_trace(model_dir, dtype, steps, out_dir, max_tokens, timeout=600):
-    """Run bin/trace_run on ``steps`` (a list of dicts); returns {step: array [wanted, vocab]}."""
+def run_trace(model_dir, dtype, steps, out_dir, max_tokens, timeout=600, random_seed=None):
+    """Run bin/trace_run on ``steps`` (a list of dicts); returns {step: array [wanted, vocab]}.
+    ``random_seed``: no checkpoint is read; ``--random <model_dir>/config.json --seed`` draws the weights."""
     out_dir = Path(out_dir)
     text = "".join(json.dumps(s) + "\n" for s in steps)
+    source = (["--model", str(model_dir)] if random_seed is None
+              else ["--random", str(Path(model_dir) / "config.json"), "--seed", str(random_seed)])
     result = subprocess.run(
-        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
+        [sys.executable, str(ROOT / "bin" / "trace_run"), *source, "--dtype", dtype,
          "--out", str(out_dir), "--max-tokens", str(max_tokens)],
         input=text, capture_output=True, text=True, timeout=timeout)
     assert result.returncode == 0, result.stderr[-4000:]

@@ -794,3 +794,48 @@ def test_attention_prefill_tcgen05_at_the_edges_of_tiles_and_windows(head_dim):
             assert torch.allclose(got, want, rtol=2e-2, atol=2e-2) == visible, (cached, window, query, far)
     torch.cuda.synchronize()
     assert int(k.error_flag.item()) == 0
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,hidden,block_size,lengths,new,rotate,write_kv", [
+    (32, 4, 64, 2048, 64, [300, 129, 65], [300, 129, 65], True, True),     # the TinyLlama layout, whole prompts
+    (5, 1, 64, 200, 16, [400, 200], [150, 110], True, True),               # a partly cached prompt, a tile that N cuts
+    (8, 2, 128, 520, 32, [257], [257], True, True),                        # head size 128: two slabs a query head
+    (6, 6, 128, 264, 64, [140, 90], [140, 90], False, True),               # no rotation
+    (4, 2, 64, 328, 16, [200], [200], True, False),                        # a layer that reads another layer's cache
+])
+def test_linear_qkv_rope_equals_the_projection_followed_by_rope_kv_write(heads, kv_heads, head_dim, hidden, block_size,
+                                                                         lengths, new, rotate, write_kv):
+    """The q|k|v projection with rotation and cache write in its epilogue against the same projection stored in float
+    followed by rope_kv_write (which has its own test against plain arithmetic): same queries, same cache rows,
+    nothing else touched."""
+    from stratakv_b200 import ops
+    from stratakv_b200.parts.position import rope_table
+    dtype = torch.bfloat16
+    k = lib(dtype, head_dim)
+    assert k.has_linear_qkv_rope()
+    setup = paged_setup(dtype, lengths, new, heads, kv_heads, head_dim, block_size, seed=heads + head_dim)
+    n = setup["positions"].numel()
+    width = (heads + 2 * kv_heads) * head_dim
+    a = torch.randn(n, hidden, device="cuda").to(dtype)
+    w = (torch.randn(width, hidden, device="cuda") / math.sqrt(hidden)).to(dtype)
+    table = torch.from_numpy(rope_table(head_dim, 25000.0, max(lengths) + 8)).cuda() if rotate else None
+    # in two steps
+    qkv = torch.empty(n, width, device="cuda")
+    k.linear(a, w, qkv, ops.MODE_STORE_F32)
+    k1, v1 = torch.full_like(setup["k_cache"], 7.0), torch.full_like(setup["v_cache"], 7.0)
+    q1 = torch.full((n, heads * head_dim), float("nan"), device="cuda").to(dtype)
+    k.rope_kv_write(qkv, table, setup["positions"], setup["token_seq"], setup["table"], q1, k1, v1, heads, kv_heads,
+                    head_dim, block_size, write_kv)
+    # in one
+    k2, v2 = torch.full_like(setup["k_cache"], 7.0), torch.full_like(setup["v_cache"], 7.0)
+    q2 = torch.full((n, heads * head_dim), float("nan"), device="cuda").to(dtype)
+    k.linear_qkv_rope(a, w, q2, table, setup["positions"], setup["token_seq"], setup["table"], k2, v2, heads, kv_heads,
+                      head_dim, block_size, write_kv)
+    torch.cuda.synchronize()
+    assert int(k.error_flag.item()) == 0
+    # the same float accumulators rotated by the same formula; the compilers may contract a*c - b*s differently
+    torch.testing.assert_close(q2.float(), q1.float(), rtol=2.0 ** -7, atol=1e-6)
+    torch.testing.assert_close(k2.float(), k1.float(), rtol=2.0 ** -7, atol=1e-6)
+    assert torch.equal(v2, v1)
+    if not write_kv:
+        assert (k2 == 7.0).all() and (v2 == 7.0).all()

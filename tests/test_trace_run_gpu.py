@@ -53,3 +53,18 @@ def test_replay_three_ways(tmp_path, dtype, name):
     for step, want in expect.items():
         rtol, atol = tolerance(dtype, want)
         np.testing.assert_allclose(got[step], want, rtol=rtol, atol=atol, err_msg=f"step {step}")
+
+
+def test_replay_with_random_weights_equals_the_folder_of_the_same_seed(tmp_path):
+    """``--random CONFIG --seed S`` draws the tensors that the random-weights mode writes to a folder for the same
+    seed, so a replay without a checkpoint gives the logits of a replay of that folder, bit for bit."""
+    folder = make_folder(tmp_path / "model", TINY["B"], seed=33, dtype="bfloat16")
+    tokens = random_tokens(TINY["B"]["vocab_size"], 20, seed=4)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:12], "want": [0, 11]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[12:13], "want": [0]}], "end": ["a"]}]
+    from_folder = run_trace(folder, "bfloat16", steps, tmp_path / "a", max_tokens=64)
+    drawn = run_trace(folder, "bfloat16", steps, tmp_path / "b", max_tokens=64, random_seed=33)
+    other = run_trace(folder, "bfloat16", steps, tmp_path / "c", max_tokens=64, random_seed=34)
+    for step in (0, 1):
+        assert np.array_equal(from_folder[step], drawn[step])
+        assert not np.array_equal(from_folder[step], other[step])
