@@ -4,12 +4,16 @@
 // It does the arithmetic of attention_prefill.cu (src/layers/attention.cpp:261-338 in the
 // reference, which has no prefill kernel at all) with another division of labour.  A block takes
 // 128 queries of one head; keys and values come in tiles of 64 positions:
-//   warp 0   one thread: TMA loads of the Q tile (once) and of K and V tiles into two-stage rings;
-//            a tile is gathered from the cache blocks the sequence's block table names;
-//   warp 1   one thread: S = Q.K^T (128 x 64 x head_dim) into one of two score buffers in tensor
-//            memory (the next tile's scores are issued before this tile's output product), and
-//            O += P.V (128 x head_dim x 64) into the output accumulator, also in tensor memory;
-//            V is used as it lies in the cache (positions x head_dim), as an MN-major operand;
+//   warp 0   keys and scores: TMA loads of the Q tile (once) and of K tiles into a ring of four stages (a tile
+//            is gathered from the cache blocks the sequence's block table names, whose entries the warp holds 32
+//            at a time in registers), and S = Q.K^T (128 x 64 x head_dim) into one of two score buffers in
+//            tensor memory, a tile ahead of the softmax;
+//   warp 1   values and output: TMA loads of V tiles into a ring of three stages, and O += P.V
+//            (128 x head_dim x 64) into the output accumulator, also in tensor memory; V is used as it lies
+//            in the cache (positions x head_dim), as an MN-major operand.
+//            Both warps walk their loops whole, and one elected lane issues.  A single issuing thread for
+//            both products measured as the limit of the kernel: its four waits and sixteen small tcgen05
+//            instructions a tile took 1,800 cycles, more than the softmax of the tile;
 //   warps 2-5  one thread per query row: read the scores with tcgen05.ld, mask, 2^x on the
 //            special-function unit (scores carry log2 e), row sums, probabilities as bfloat16 into
 //            one of two swizzled shared-memory tiles (the A operand of P.V).  The maximum the
@@ -60,6 +64,12 @@ __device__ __forceinline__ bool a_wait(uint32_t bar, uint32_t parity, int* flag)
     if (flag) atomicOr(flag, 4);
     return false;
 }
+// One lane of a converged warp (the compiler can then keep what the issuing lane computes in uniform registers)
+__device__ __forceinline__ bool a_elect() {
+    uint32_t chosen;
+    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(chosen));
+    return chosen != 0;
+}
 __device__ __forceinline__ void a_tma(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -100,6 +110,12 @@ __device__ __forceinline__ float a_exp2(float x) {
     return y;
 }
 
+__device__ __forceinline__ float a_max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
+
 __device__ __forceinline__ void a_st32(uint32_t taddr, const uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -112,8 +128,13 @@ __device__ __forceinline__ void a_st32(uint32_t taddr, const uint32_t (&v)[32]) 
         : "memory");
 }
 
-// barriers: Q; for each of two stages K full/empty, V full/empty, S full/empty, P full/empty
-enum { B_Q = 0, B_KF = 1, B_KE = 3, B_VF = 5, B_VE = 7, B_SF = 9, B_SE = 11, B_PF = 13, B_PE = 15, B_COUNT = 17 };
+// Keys come through a ring of four tiles and values through one of three, both asked for two tiles ahead (a stage of
+// keys is known to be free when the softmax has taken the scores of its tile, a stage of values when the product after
+// it has been seen complete); scores and probabilities have two buffers each.
+constexpr int K_STAGES = 4, V_STAGES = 3;
+// barriers: Q; K full and V full for each stage of the rings; S full/empty and P full/empty for each buffer
+enum { B_Q = 0, B_KF = 1, B_VF = B_KF + K_STAGES, B_SF = B_VF + V_STAGES, B_SE = B_SF + 2, B_PF = B_SE + 2, B_PE = B_PF + 2,
+       B_COUNT = B_PE + 2 };
 
 // The running maximum a row's exponentials are taken against is only raised when a tile's maximum
 // exceeds it by more than this many powers of two; until then the accumulated output (in tensor
@@ -129,9 +150,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     extern __shared__ uint8_t a_raw[];
     uint8_t* base = (uint8_t*)(((uintptr_t)a_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_tile = base;                                        // ACH tiles of 128 rows
-    uint8_t* k_ring = q_tile + ACH * TILE_BYTES;                   // 2 stages x ACH tiles of 64 rows
-    uint8_t* v_ring = k_ring + 2 * ACH * KV_TILE_BYTES;            // 2 stages x ACH tiles of 64 rows
-    uint8_t* p_ring = v_ring + 2 * ACH * KV_TILE_BYTES;            // 2 tiles of 128 rows (64 keys = 128 bytes a row)
+    uint8_t* k_ring = q_tile + ACH * TILE_BYTES;                   // K_STAGES stages x ACH tiles of 64 rows
+    uint8_t* v_ring = k_ring + K_STAGES * ACH * KV_TILE_BYTES;     // V_STAGES stages x ACH tiles of 64 rows
+    uint8_t* p_ring = v_ring + V_STAGES * ACH * KV_TILE_BYTES;            // 2 tiles of 128 rows (64 keys = 128 bytes a row)
     uint64_t* bars = (uint64_t*)(p_ring + 2 * TILE_BYTES);
     uint32_t* tmem_slot = (uint32_t*)(bars + B_COUNT);
     const uint32_t bar0 = a_smem(bars);
@@ -156,8 +177,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (threadIdx.x == 0) {
         a_init(bar(B_Q), 1);
+        for (int i = 0; i < K_STAGES; ++i) a_init(bar(B_KF, i), 1);
+        for (int i = 0; i < V_STAGES; ++i) a_init(bar(B_VF, i), 1);
         for (int i = 0; i < 2; ++i) {
-            a_init(bar(B_KF, i), 1); a_init(bar(B_KE, i), 1); a_init(bar(B_VF, i), 1); a_init(bar(B_VE, i), 1);
             a_init(bar(B_SF, i), 1); a_init(bar(B_SE, i), 4); a_init(bar(B_PF, i), 4); a_init(bar(B_PE, i), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -174,71 +196,107 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t tmem_s = tmem, tmem_o = tmem + 128;             // S: 2 x 64 columns; O: AHD columns
     pdl_wait();                                                    // q and the cache rows come from the kernels before
 
-    if (warp == 0 && lane == 0) {
-        // ---- loader ------------------------------------------------------------------------------
-        a_expect(bar(B_Q), ACH * TILE_BYTES);
-        for (int c = 0; c < ACH; ++c)
-            a_tma(a_smem(q_tile + c * TILE_BYTES), &map_q, head * AHD + 64 * c, q_begin + tile * ABM, bar(B_Q));
-        const int* table = block_table + (size_t)seq * table_width;
-        bool ok = true;
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int s = j & 1;
-            const int key0 = (first_tile + j) * ABN;
-            for (int which = 0; which < 2 && ok; ++which) {           // 0: keys, 1: values
-                const uint32_t full = bar(which ? B_VF : B_KF, s), empty = bar(which ? B_VE : B_KE, s);
-                if (j >= 2) ok = a_wait(empty, ((j >> 1) - 1) & 1, flag);
-                if (!ok) break;
-                uint8_t* dst = (which ? v_ring : k_ring) + (size_t)s * ACH * KV_TILE_BYTES;
-                a_expect(full, ACH * KV_TILE_BYTES);
-                for (int r = 0; r < ABN; r += rows_per_load) {
-                    const int key = key0 + r;
-                    const int block = table[min(key / block_size, table_width - 1)];
-                    const int row = (block * num_kv_heads + kv_head) * block_size + (key % block_size);
-                    for (int c = 0; c < ACH; ++c)
-                        a_tma(a_smem(dst + c * KV_TILE_BYTES + r * 128), which ? &map_v : &map_k, 64 * c, row, full);
-                }
+    // Cache rows of a tile of 64 keys, for the copies of either warp below: the block table's entries come 32 at a time
+    // into one register per lane (a look-up per tile by the issuing lane alone would put the latency of a read from
+    // global memory into every round of its loop).
+    const int* table = block_table + (size_t)seq * table_width;
+    int cached_from = -1, cached_entry = 0;
+    auto cache_row = [&](int key) {                                    // called by the whole warp
+        const int entry = key / block_size;
+        if (cached_from < 0 || entry < cached_from || entry >= cached_from + 32) {
+            cached_from = entry;
+            cached_entry = table[min(entry + lane, table_width - 1)];
+        }
+        const int block = __shfl_sync(0xffffffffu, cached_entry, entry - cached_from);
+        return (block * num_kv_heads + kv_head) * block_size + (key % block_size);
+    };
+    auto load_tile = [&](int which, int t) {                           // 0: keys, 1: values; tile t of this block
+        const int st = which ? t % V_STAGES : t % K_STAGES;
+        const uint32_t full = bar(which ? B_VF : B_KF, st);
+        uint8_t* dst = (which ? v_ring : k_ring) + (size_t)st * ACH * KV_TILE_BYTES;
+        const int key0 = (first_tile + t) * ABN;
+        const bool issuer = a_elect();
+        if (issuer) a_expect(full, ACH * KV_TILE_BYTES);
+        for (int r = 0; r < ABN; r += rows_per_load) {
+            const int row = cache_row(key0 + r);
+            if (issuer) {
+                for (int c = 0; c < ACH; ++c)
+                    a_tma(a_smem(dst + c * KV_TILE_BYTES + r * 128), which ? &map_v : &map_k, 64 * c, row, full);
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- tensor-core issue -----------------------------------------------------------------------
-        constexpr uint32_t idesc_s = a_idesc(ABM, ABN, 0), idesc_o = a_idesc(ABM, 64, 1);
+        __syncwarp();
+    };
+    if (warp == 0) {
+        // ---- keys and scores: the whole warp walks the loop, one elected lane issues -----------------------
+        // For tile i: wait until softmax i - 2 has taken its scores out of the buffer (which also says that the
+        // product of tile i - 2 is complete and its keys' stage free), and for the keys of tile i; issue
+        // S[i & 1] = Q . K_i^T; then ask for the keys of tile i + 2, into the stage of tile i - 2.
+        if (a_elect()) {
+            a_expect(bar(B_Q), ACH * TILE_BYTES);
+            for (int c = 0; c < ACH; ++c)
+                a_tma(a_smem(q_tile + c * TILE_BYTES), &map_q, head * AHD + 64 * c, q_begin + tile * ABM, bar(B_Q));
+        }
+        __syncwarp();
+        for (int t = 0; t < 2 && t < n_tiles; ++t) load_tile(0, t);
+        constexpr uint32_t idesc_s = a_idesc(ABM, ABN, 0);
         bool ok = a_wait(bar(B_Q), 0, flag);
-        auto issue_s = [&](int j) {                                  // S[j & 1] = Q . K_j^T
-            const int s = j & 1;
-            if (!a_wait(bar(B_KF, s), (j >> 1) & 1, flag)) return false;
-            if (j >= 2 && !a_wait(bar(B_SE, s), ((j >> 1) - 1) & 1, flag)) return false;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < ACH; ++c) {
-                const uint64_t qd = a_desc(a_smem(q_tile + c * TILE_BYTES));
-                const uint64_t kd = a_desc(a_smem(k_ring + (size_t)(s * ACH + c) * KV_TILE_BYTES));
-#pragma unroll
-                for (int k = 0; k < 4; ++k) a_mma(tmem_s + 64u * s, qd + 2 * k, kd + 2 * k, idesc_s, (c | k) ? 1u : 0u);
-            }
-            a_commit(bar(B_KE, s));
-            a_commit(bar(B_SF, s));
-            return true;
-        };
-        if (ok && n_tiles > 0) ok = issue_s(0);
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int s = j & 1;
-            if (j + 1 < n_tiles) ok = issue_s(j + 1);                 // the next scores run under this tile's softmax
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int s = i & 1, ks = i % K_STAGES;
+            if (i >= 2) ok = a_wait(bar(B_SE, s), ((i >> 1) - 1) & 1, flag);
+            if (ok) ok = a_wait(bar(B_KF, ks), (i / K_STAGES) & 1, flag);
             if (!ok) break;
-            // O += P_j . V_j once the probabilities and the values are in shared memory
-            if (!a_wait(bar(B_PF, s), (j >> 1) & 1, flag) || !a_wait(bar(B_VF, s), (j >> 1) & 1, flag)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int kk = 0; kk < ABN / 16; ++kk) {                   // 16 keys per instruction
-                const uint64_t pd = a_desc(a_smem(p_ring + s * TILE_BYTES)) + 2 * kk;
+            if (a_elect()) {
 #pragma unroll
                 for (int c = 0; c < ACH; ++c) {
-                    // V tile rows are keys: 16 keys further is 16 x 128 bytes = 128 descriptor units
-                    const uint64_t vd = a_desc(a_smem(v_ring + (size_t)(s * ACH + c) * KV_TILE_BYTES)) + 128 * kk;
-                    a_mma(tmem_o + (uint32_t)(64 * c), pd, vd, idesc_o, (j | kk) ? 1u : 0u);
+                    const uint64_t qd = a_desc(a_smem(q_tile + c * TILE_BYTES));
+                    const uint64_t kd = a_desc(a_smem(k_ring + (size_t)(ks * ACH + c) * KV_TILE_BYTES));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) a_mma(tmem_s + 64u * s, qd + 2 * k, kd + 2 * k, idesc_s, (c | k) ? 1u : 0u);
                 }
+                a_commit(bar(B_SF, s));
             }
-            a_commit(bar(B_VE, s));
-            a_commit(bar(B_PE, s));                                   // also: the output holds tiles 0..j now
+            __syncwarp();
+            if (i + 2 < n_tiles) load_tile(0, i + 2);
+        }
+        if (!ok) {
+            // a wait gave up: let the copies in flight land (microseconds) before the block may leave
+            for (int t = 0; t < 64; ++t) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        // ---- values and output products: O += P_j . V_j once the probabilities and the values are in shared
+        // memory; then the values of tile j + 2 are asked for, into the stage of tile j - 1, whose product (issued
+        // a round ago) has to be complete.
+        constexpr uint32_t idesc_o = a_idesc(ABM, 64, 1);
+        for (int t = 0; t < 2 && t < n_tiles; ++t) load_tile(1, t);
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j & 1, vs = j % V_STAGES;
+            ok = a_wait(bar(B_VF, vs), (j / V_STAGES) & 1, flag) && a_wait(bar(B_PF, s), (j >> 1) & 1, flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (a_elect()) {
+#pragma unroll
+                for (int kk = 0; kk < ABN / 16; ++kk) {               // 16 keys per instruction
+                    const uint64_t pd = a_desc(a_smem(p_ring + s * TILE_BYTES)) + 2 * kk;
+#pragma unroll
+                    for (int c = 0; c < ACH; ++c) {
+                        // V tile rows are keys: 16 keys further is 16 x 128 bytes = 128 descriptor units
+                        const uint64_t vd = a_desc(a_smem(v_ring + (size_t)(vs * ACH + c) * KV_TILE_BYTES)) + 128 * kk;
+                        a_mma(tmem_o + (uint32_t)(64 * c), pd, vd, idesc_o, (j | kk) ? 1u : 0u);
+                    }
+                }
+                a_commit(bar(B_PE, s));                               // the output holds tiles 0..j; V_j and P_j are free
+            }
+            __syncwarp();
+            if (j + 2 < n_tiles) {
+                if (j >= 1) ok = a_wait(bar(B_PE, (j - 1) & 1), ((j - 1) >> 1) & 1, flag);
+                if (!ok) break;
+                load_tile(1, j + 2);
+            }
+        }
+        if (!ok) {
+            for (int t = 0; t < 64; ++t) __nanosleep(1000);
         }
     } else if (warp >= 2) {
         // ---- softmax and output: one thread per query row -----------------------------------------
@@ -280,7 +338,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int e = 0; e < ABN; ++e) m4[e & 3] = fmaxf(m4[e & 3], sc[e]);
+            for (int e = 0; e < ABN; e += 8) {                         // (three-input maxima: two scores an instruction)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) m4[c] = a_max3(m4[c], sc[e + 2 * c], sc[e + 2 * c + 1]);
+            }
             const float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;   // scale > 0
             // raise the maximum in use (and rescale what has been accumulated) only when it matters
             const bool raise = tile_max > used_max + RESCALE_MARGIN;
@@ -314,8 +375,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 float p[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const float x = sc[8 * piece + e];
-                    p[e] = (plain || x != -INFINITY) ? a_exp2(fmaf(x, scale_log2, -offset)) : 0.0f;
+                    // (a masked score is -infinity, the offset is finite and the scale positive: 2^-infinity = 0)
+                    p[e] = a_exp2(fmaf(sc[8 * piece + e], scale_log2, -offset));
                     s4[e & 3] += p[e];
                 }
                 uint32_t packed[4];
@@ -440,7 +501,7 @@ SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, cons
     const int tiles_per_seq = (max_q_len + ABM - 1) / ABM;
     const long long blocks = (long long)n_seqs * tiles_per_seq;
     if (blocks > 65535) return fail("skv_attention_prefill_tc", "too many query tiles in one step (65,535 at most)");
-    const size_t smem = (size_t)(ACH + 2) * TILE_BYTES + (size_t)4 * ACH * KV_TILE_BYTES + B_COUNT * 8 + 16 + 1024;
+    const size_t smem = (size_t)(ACH + 2) * TILE_BYTES + (size_t)(K_STAGES + V_STAGES) * ACH * KV_TILE_BYTES + B_COUNT * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
         const cudaError_t status = cudaFuncSetAttribute(prefill_attention_tc_kernel,

@@ -536,6 +536,190 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// ---- pairs of blocks: one 256 x 256 tile per two SMs ------------------------------------------------
+// A block of the kernel above has to fetch 48 KB (128 rows of A and 256 of W, 64 wide) for 512 cycles of tensor
+// work, 96 bytes a cycle, and an SM takes in about 64: its tensor pipe measured busy two thirds of the time.  Here
+// two blocks of a cluster share a tile of 256 x 256: each fetches its 128 rows of A and its half (128 rows) of W,
+// 32 KB for the same 512 cycles, and one thread of the first block issues tcgen05.mma.cta_group::2, which reads both
+// halves of W from the two blocks' shared memory and leaves each block its 128 rows of the result in its own
+// tensor memory.  The copies of both blocks complete on the first block's barriers (it expects the bytes of
+// both); a commit frees a stage, or hands over an accumulator, in both blocks at once; the epilogue warps of both
+// blocks return an accumulator to the first block's issuer.  The epilogue itself is the one of the kernel above.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+// The address, in the cluster's shared window, of what lies at `addr` in block `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_address(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    return remote;
+}
+
+// A copy into this block's shared memory whose bytes count on a barrier of the pair's first block
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t first_block_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(first_block_bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives, when the MMAs issued so far have finished, on the barrier at this offset in both blocks of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(both) : "memory");
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
+                         int N, int K, int mode, int act, int* __restrict__ flag, const RopeArgs rope) {
+    constexpr int BN = 256;                                  // the pair's tile: 256 rows (128 per block) x 256 columns
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = (BN / 2) * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
+    constexpr uint32_t TMEM_COLS = 512, ACC_STRIDE = 256;
+    constexpr uint32_t SLAB_BYTES = 4 * 2 * 4096;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* slab_base = tiles + (size_t)STAGES * STAGE_BYTES;
+    uint64_t* bars = (uint64_t*)(slab_base + SLAB_BYTES);   // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                   // 0: the block that issues the pair's MMAs
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int k_iters = (K + TC_BK - 1) / TC_BK;
+    const int m_tiles = (M + 2 * TC_BM - 1) / (2 * TC_BM), n_tiles = (N + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
+    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
+    const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        // full and acc_empty are used in the first block only: one arrival (its loader's, with the bytes of both
+        // blocks) and one per epilogue warp of both blocks
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_addr(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    // both blocks' barriers exist before either signals the other's
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        // ---- loader: this block's rows of A and its half of the W rows ------------------------------
+        bool ok = true;
+        int it = 0;
+        const uint32_t first_full0 = cluster_address(full0, 0);
+        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+            const int m0 = (tile % m_tiles) * 2 * TC_BM + (int)rank * TC_BM;
+            const int w0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+            for (int i = 0; i < k_iters; ++i, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, flag);
+                if (!ok) break;
+                const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                tma_load_2d_pair(a_dst, &map_a, i * TC_BK, m0, first_full0 + 8 * s);
+                tma_load_2d_pair(a_dst + A_BYTES, &map_w, i * TC_BK, w0, first_full0 + 8 * s);
+            }
+        }
+        if (!ok && rank == 0) {
+            // let the copies in flight land before the pair leaves (bounded); the other block waits for this
+            // one at the cluster barrier below
+            for (int i = max(0, it - STAGES); i < it; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr);
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---- tensor-core issue, for both blocks -------------------------------------------------------
+        constexpr uint32_t idesc = umma_idesc(2 * TC_BM, BN);
+        bool ok = true;
+        int it = 0, local = 0;
+        for (int tile = pair; tile < total_tiles && ok; tile += pairs, ++local) {
+            const int buf = local & 1;
+            if (local >= 2) {
+                ok = mbar_wait(acc_empty0 + 8 * buf, ((local >> 1) - 1) & 1, flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            const uint32_t acc = tmem_base + (uint32_t)buf * ACC_STRIDE;
+            for (int i = 0; i < k_iters; ++i, ++it) {
+                const int s = it % STAGES;
+                ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                const uint64_t a_desc = umma_desc(a_addr), w_desc = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    umma_bf16_pair(acc, a_desc + 2 * k, w_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit_pair(empty0 + 8 * s);
+            }
+            if (ok) umma_commit_pair(acc_full0 + 8 * buf);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue: this block's 128 rows of the tile ------------------------------------------
+        const int quarter = warp & 3;
+        uint8_t* slabs = slab_base + quarter * 8192;
+        int buffer = 0, local = 0;
+        bool ok = true;
+        const uint32_t first_acc_empty0 = cluster_address(acc_empty0, 0);
+        for (int tile = pair; tile < total_tiles && ok; tile += pairs, ++local) {
+            const int buf = local & 1;
+            ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int m0 = (tile % m_tiles) * 2 * TC_BM + (int)rank * TC_BM, n0 = (tile / m_tiles) * BN;
+            if (mode == TC_MODE_QKV_ROPE) {
+                epilogue_tile_rope<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, rope,
+                                       M, N, m0, n0);
+            } else {
+                epilogue_tile<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, tma_out, out,
+                                  M, N, mode, act, m0, n0);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];"
+                             ::"r"(first_acc_empty0 + 8 * buf) : "memory");
+        }
+        if (tma_out) {
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            __syncwarp();
+        }
+    }
+    // neither block leaves, or frees its tensor memory, while the other may still read its shared memory or
+    // signal its barriers
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- few tokens: the weights take the 128 rows of the instruction ---------------------------------
 // For steps of 17 to 128 tokens the tile above would use a fraction of its 128 token rows and leave most SMs
 // without a tile.  Here the operands change places: D^T[128 weight rows, tokens] = W_tile . X^T, so a block
@@ -831,6 +1015,89 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
                       map_a, map_w, map_out, tma_out, out, M, N, K, mode, act, flag, rope);
 }
 
+// The two-block form: clusters of two blocks, as many as the GPU runs at once (74 on 148 SMs), walk the 256 x 256 tiles.
+constexpr int PAIR_STAGES = 6;
+constexpr size_t PAIR_SMEM = (size_t)PAIR_STAGES * (TC_BM * TC_BK * 2 + 128 * TC_BK * 2) + 4 * 2 * 4096 +
+                             (2 * PAIR_STAGES + 4) * 8 + 16 + 1024;
+
+static void pair_launch_config(cudaLaunchConfig_t* config, cudaLaunchAttribute* attributes, cudaStream_t stream) {
+    *config = cudaLaunchConfig_t{};
+    config->blockDim = dim3(TC_THREADS);
+    config->dynamicSmemBytes = PAIR_SMEM;
+    config->stream = stream;
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 2;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config->attrs = attributes;
+    config->numAttrs = 1;
+}
+
+// How many pairs of blocks the GPU runs at once (0: this GPU cannot run the two-block kernel; it is not used then)
+static int pair_slots() {
+    static int slots = -1;
+    if (slots < 0) {
+        slots = 0;
+        cudaLaunchConfig_t config;
+        cudaLaunchAttribute attributes[2];
+        pair_launch_config(&config, attributes, nullptr);
+        config.gridDim = dim3((unsigned)(tc_sm_count() / 2 * 2));
+        int clusters = 0;
+        if (tc_sm_count() >= 2 &&
+            cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)PAIR_SMEM) == cudaSuccess &&
+            cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<PAIR_STAGES>, &config) == cudaSuccess && clusters > 0)
+            slots = clusters < tc_sm_count() / 2 ? clusters : tc_sm_count() / 2;
+        else
+            cudaGetLastError();                    // (the refusal is an answer, not an error of the caller's)
+    }
+    return slots;
+}
+
+static int launch_pair(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
+                       cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
+    CUtensorMap map_a, map_w, map_out;
+    if (int code = tensor_map(a, M, K, 2, TC_BM, TC_BK, &map_a)) return code;
+    if (int code = tensor_map(w, N, K, 2, 128, TC_BK, &map_w)) return code;
+    const bool float_out = mode == TC_MODE_STORE_F32 || mode == TC_MODE_ADD_F32;
+    const int out_cols = mode == TC_MODE_GATED ? N / 2 : (mode == TC_MODE_QKV_ROPE ? rope.num_heads * rope.head_dim : N);
+    const int out_elem = float_out ? 4 : 2;
+    int tma_out = ((size_t)out_cols * out_elem) % 16 == 0 && ((uintptr_t)out & 15) == 0 ? 1 : 0;
+    if (mode == TC_MODE_QKV_ROPE && !tma_out) return fail("skv_linear_qkv_rope", "the queries' rows must be 16-byte multiples");
+    if (tma_out) {
+        if (int code = tensor_map(out, M, out_cols, out_elem, 32, float_out ? 32 : 64, &map_out)) return code;
+    } else {
+        map_out = map_a;
+    }
+    const int slots = pair_slots();
+    if (slots <= 0) return fail("skv_linear(tcgen05 pair)", "this GPU runs no cluster of two such blocks");
+    cudaLaunchConfig_t config;
+    cudaLaunchAttribute attributes[2];
+    pair_launch_config(&config, attributes, stream);
+    const long long tiles = (long long)((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + 255) / 256);
+    config.gridDim = dim3(2u * (unsigned)(tiles < slots ? tiles : slots));
+    config.numAttrs = pdl_enabled() ? 2 : 1;
+    const cudaError_t status = cudaLaunchKernelEx(&config, gemm_tcgen05_pair_kernel<PAIR_STAGES>, map_a, map_w, map_out,
+                                                  tma_out, out, M, N, K, mode, act, flag, rope);
+    if (status != cudaSuccess) return fail("skv_linear(tcgen05 pair)", cudaGetErrorString(status));
+    return 0;
+}
+
+// Whether the two-block kernel is the cheaper one, in the units of the cost of a width below (rounds x 256 columns):
+// measured against 256-wide tiles of one block it is 4-6 % faster where the main loop dominates (2,048 x 11,264 x 2,048:
+// 71.3 -> 67.7 us; 2,048 x 2,048 x 5,632: 36.5 -> 34.9; 8,192 cubed: 806 -> 768, the library GEMM 779-816) and 4 %
+// slower where a block has one short tile (2,048 x 2,048 x 2,048: 16.0 -> 16.6 us; a pair's set-up is heavier).
+static double pair_cost(int M, int N, int K) {
+    const int slots = pair_slots();
+    if (slots <= 0 || N <= 128) return 1e30;
+    const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+    const long long rounds = (tiles + slots - 1) / slots;
+    if (rounds * ((K + TC_BK - 1) / TC_BK) < 80) return 1e30;
+    return (double)rounds * 256 / 1.04;
+}
+
 template <int MP, int STAGES>
 static int launch_few_tokens(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                              int* flag, cudaStream_t stream) {
@@ -878,21 +1145,17 @@ static int launch_few_tokens(const void* a, const void* w, void* out, int M, int
     return 0;
 }
 
-int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
-                   cudaStream_t stream) {
-    if (K % 8 != 0) return fail("skv_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
-    if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_linear(tcgen05)", "operands must be 16-byte aligned");
-    if (mode == TC_MODE_GATED && N % 16 != 0) return fail("skv_linear(tcgen05)", "a gated weight needs a multiple of 16 rows");
-    if (M <= 32) return launch_few_tokens<32, 8>(a, w, out, M, N, K, mode, act, flag, stream);
-    if (M <= 64) return launch_few_tokens<64, 8>(a, w, out, M, N, K, mode, act, flag, stream);
-    if (M <= 128) return launch_few_tokens<128, 6>(a, w, out, M, N, K, mode, act, flag, stream);
-    // Wider tiles re-read less of A and W from L2 per flop (measured at 2,048 x 6,144 x 4,096: 1,268 TFLOP/s with
-    // 256-wide tiles, 1,014 with 160, 860 with 128); narrow ones waste less on small N and fill the last round of
-    // tiles better: 2,048 tokens x 2,560 columns are 160 tiles of 256 columns (two rounds on 148 SMs, the second nearly
-    // empty: 27.9 us) but 256 tiles of 160 (two rounds of five eighths the work: 25.6 us).  Cost of a width: rounds x
-    // width / efficiency per flop.  A width of 160
-    // serves the float epilogues only (its slabs of 32 columns divide it; the 64- and 128-column slabs of the
-    // other two modes do not).
+// Which kernel serves a shape.  Up to 128 tokens the few-token kernel.  Above, a tile form by cost: wider tiles re-read
+// less of A and W from L2 per flop (measured at 2,048 x 6,144 x 4,096: 1,268 TFLOP/s with 256-wide tiles, 1,014 with
+// 160, 860 with 128); narrow ones waste less on small N and fill the last round of tiles better: 2,048 tokens x
+// 2,560 columns are 160 tiles of 256 columns (two rounds on 148 SMs, the second nearly empty: 27.9 us) but 256 tiles of
+// 160 (two rounds of five eighths the work: 25.6 us).  Cost of a width: rounds x width / efficiency per flop.  A width
+// of 160 serves the float epilogues only (its slabs of 32 columns divide it; the 64- and 128-column slabs of the
+// other modes do not).
+enum { FORM_FEW_TOKENS = 0, FORM_128 = 1, FORM_160 = 2, FORM_256 = 3, FORM_PAIR = 4 };
+
+static int choose_form(int M, int N, int K, int mode) {
+    if (M <= 128) return FORM_FEW_TOKENS;
     const long long m_tiles = (M + 127) / 128;
     auto cost = [&](int width, double efficiency) {
         const long long tiles = m_tiles * ((N + width - 1) / width);
@@ -901,9 +1164,26 @@ int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K,
     const bool float_out = mode == TC_MODE_STORE_F32 || mode == TC_MODE_ADD_F32;
     const double wide = N > 128 ? cost(256, 1.0) : 1e30, narrow = cost(128, 0.68);
     const double middle = (float_out && N > 128) ? cost(160, 0.80) : 1e30;
-    if (middle < wide && middle < narrow) return launch_tc<160, 5>(a, w, out, M, N, K, mode, act, flag, stream);
-    if (wide <= narrow) return launch_tc<256, 4>(a, w, out, M, N, K, mode, act, flag, stream);
-    return launch_tc<128, 4>(a, w, out, M, N, K, mode, act, flag, stream);
+    const double paired = pair_cost(M, N, K);
+    if (paired < wide && paired < middle && paired < narrow) return FORM_PAIR;
+    if (middle < wide && middle < narrow) return FORM_160;
+    return wide <= narrow ? FORM_256 : FORM_128;
+}
+
+int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act, int* flag,
+                   cudaStream_t stream) {
+    if (K % 8 != 0) return fail("skv_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
+    if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_linear(tcgen05)", "operands must be 16-byte aligned");
+    if (mode == TC_MODE_GATED && N % 16 != 0) return fail("skv_linear(tcgen05)", "a gated weight needs a multiple of 16 rows");
+    if (M <= 32) return launch_few_tokens<32, 8>(a, w, out, M, N, K, mode, act, flag, stream);
+    if (M <= 64) return launch_few_tokens<64, 8>(a, w, out, M, N, K, mode, act, flag, stream);
+    if (M <= 128) return launch_few_tokens<128, 6>(a, w, out, M, N, K, mode, act, flag, stream);
+    switch (choose_form(M, N, K, mode)) {
+        case FORM_PAIR: return launch_pair(a, w, out, M, N, K, mode, act, flag, stream);
+        case FORM_160: return launch_tc<160, 5>(a, w, out, M, N, K, mode, act, flag, stream);
+        case FORM_256: return launch_tc<256, 4>(a, w, out, M, N, K, mode, act, flag, stream);
+        default: return launch_tc<128, 4>(a, w, out, M, N, K, mode, act, flag, stream);
+    }
 }
 
 // The q|k|v projection of a step with many tokens, with the rotary encoding and the cache write in its epilogue.
@@ -918,14 +1198,11 @@ int linear_tcgen05_qkv_rope(const void* a, const void* w, void* q_out, int M, in
     if (rope.num_heads <= 0 || rope.num_kv_heads <= 0 || N != (rope.num_heads + 2 * rope.num_kv_heads) * rope.head_dim)
         return fail("skv_linear_qkv_rope", "the weight's rows must be [query heads | key heads | value heads]");
     if (rope.block_size <= 0 || rope.table_width <= 0) return fail("skv_linear_qkv_rope", "bad cache block size or table width");
-    const long long m_tiles = (M + 127) / 128;
-    auto cost = [&](int width, double efficiency) {
-        const long long tiles = m_tiles * ((N + width - 1) / width);
-        return (double)((tiles + tc_sm_count() - 1) / tc_sm_count()) * width / efficiency;
-    };
-    if (cost(256, 1.0) <= cost(128, 0.68))
-        return launch_tc<256, 4>(a, w, q_out, M, N, K, TC_MODE_QKV_ROPE, 0, flag, stream, rope);
-    return launch_tc<128, 4>(a, w, q_out, M, N, K, TC_MODE_QKV_ROPE, 0, flag, stream, rope);
+    switch (choose_form(M, N, K, TC_MODE_QKV_ROPE)) {
+        case FORM_PAIR: return launch_pair(a, w, q_out, M, N, K, TC_MODE_QKV_ROPE, 0, flag, stream, rope);
+        case FORM_256: return launch_tc<256, 4>(a, w, q_out, M, N, K, TC_MODE_QKV_ROPE, 0, flag, stream, rope);
+        default: return launch_tc<128, 4>(a, w, q_out, M, N, K, TC_MODE_QKV_ROPE, 0, flag, stream, rope);
+    }
 }
 
 }  // namespace skv
@@ -933,6 +1210,11 @@ int linear_tcgen05_qkv_rope(const void* a, const void* w, void* q_out, int M, in
 using namespace skv;
 
 SKV_EXPORT int skv_has_linear_qkv_rope() { return 1; }
+
+// Which of the tensor-memory kernels serves a projection of this shape and epilogue on this GPU (0 the few-token
+// kernel, 1-3 tiles of 128, 160 and 256 columns, 4 the two-block kernel): for tests, which have to know that the
+// shapes they bring reach every one of them.
+SKV_EXPORT int skv_linear_tcgen05_form(int M, int N, int K, int mode) { return choose_form(M, N, K, mode); }
 
 // out q [M, heads x head_dim] bfloat16 = rotated (a[M, K] . w[N, K]^T)[:, query columns]; keys (rotated) and values
 // of token m go to the cache row of position positions[m] of sequence token_seq[m] if write_kv.  See RopeArgs.
@@ -960,6 +1242,8 @@ SKV_EXPORT int skv_linear_qkv_rope(const void* a, const void* w, void* q_out, in
 #else
 
 SKV_EXPORT int skv_has_linear_qkv_rope() { return 0; }
+
+SKV_EXPORT int skv_linear_tcgen05_form(int, int, int, int) { return -1; }
 
 SKV_EXPORT int skv_linear_qkv_rope(const void*, const void*, void*, int, int, int, const float*, const int*, const int*,
                                    const int*, int, void*, void*, int, int, int, int, int, int*, cudaStream_t) {

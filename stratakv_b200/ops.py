@@ -15,6 +15,7 @@ from .csrc.build import BuildError, build_library
 from .residual import COLUMNS_PER_PARTIAL, KERNEL_FOLD_ROWS, NormedRows
 
 MODE_STORE, MODE_STORE_F32, MODE_ADD_F32, MODE_GATED = 0, 1, 2, 3
+MODE_QKV_ROPE = 4          # (linear_qkv_rope's own epilogue; named for Kernels.linear_form)
 # activations of a gated feed-forward's gate that every projection kernel implements (csrc/common.cuh)
 ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1}
 _DTYPE_NAMES = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
@@ -198,6 +199,12 @@ class Kernels:
 
     def has_linear_qkv_rope(self) -> bool:
         return bool(self.lib.skv_has_linear_qkv_rope())
+
+    def linear_form(self, M: int, N: int, K: int, mode: int) -> str:
+        """Which tensor-memory kernel serves a projection of this shape and epilogue on this GPU (``mode`` 4 is the
+        q|k|v projection with the rotary epilogue); for tests that must reach each of them."""
+        code = int(self.lib.skv_linear_tcgen05_form(int(M), int(N), int(K), int(mode)))
+        return {0: "few_tokens", 1: "tile_128", 2: "tile_160", 3: "tile_256", 4: "pair_256"}.get(code, "none")
 
     def linear_qkv_rope(self, a, w, q_out, cos_sin, positions, token_seq, block_table, k_cache, v_cache,
                         num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, write_kv: bool, flag=None):

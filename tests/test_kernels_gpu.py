@@ -144,6 +144,10 @@ def _products(a, w, chunk=512):
     (1000, 4112, 1032, "store_f32 store add gated"),  # tails in M, N and K at once
     (2048, 2500, 2048, "store_f32 add"),             # 160-wide tiles (256 of them, five stages), the last one clipped
     (1500, 2501, 520, "store_f32 store add"),        # 160-wide tiles whose rows the threads store themselves
+    (1000, 4112, 5200, "store_f32 store add gated"),  # pairs of blocks on 256 x 256 tiles: tails in M (the pair's second
+                                                     # block has 104 live rows in the last tile), N and K at once
+    (1100, 2560, 6000, "store gated"),               # pairs: the second block of the last row tile has no live row
+    (1500, 2501, 5208, "store_f32 store add"),       # pairs whose rows the threads store themselves
 ])
 def test_linear_tiled_tensor_memory_kernel_at_model_sizes(M, N, K, modes):
     """tests/gemv_smoke.cu:329-357 takes the reference's kernels to the model's shapes with a bound from
@@ -182,6 +186,26 @@ def test_linear_tiled_tensor_memory_kernel_at_model_sizes(M, N, K, modes):
                 assert ((out.double() - want).abs() <= slack).all(), (mode, activation)
         torch.cuda.synchronize()
         assert int(k.error_flag.item()) == 0
+
+
+def test_the_shapes_of_these_tests_reach_every_tensor_memory_kernel():
+    """The launcher picks a kernel by a cost rule; if the rule moved, the tests above and below could lose a kernel
+    without failing.  On a GPU of 148 SMs these shapes, which those tests bring, go where their comments say."""
+    from stratakv_b200 import ops
+    k = lib(torch.bfloat16)
+    if torch.cuda.get_device_properties(0).multi_processor_count != 148:
+        pytest.skip("the expectations are those of 148 SMs")
+    assert k.linear_form(100, 2048, 2048, ops.MODE_STORE) == "few_tokens"
+    assert k.linear_form(129, 2048, 2048, ops.MODE_STORE) == "tile_128"
+    assert k.linear_form(2048, 2500, 2048, ops.MODE_ADD_F32) == "tile_160"
+    assert k.linear_form(2048, 2560, 2048, ops.MODE_STORE) == "tile_256"
+    assert k.linear_form(2048, 2560, 2048, ops.MODE_QKV_ROPE) == "tile_256"
+    assert k.linear_form(2048, 2048, 2048, ops.MODE_ADD_F32) == "tile_256"      # one short tile a block: no pair
+    for M, N, K, mode in [(2048, 11264, 2048, ops.MODE_GATED), (2048, 2048, 5632, ops.MODE_ADD_F32),
+                          (1000, 4112, 5200, ops.MODE_GATED), (1000, 4112, 5200, ops.MODE_STORE),
+                          (1100, 2560, 6000, ops.MODE_STORE), (1500, 2501, 5208, ops.MODE_ADD_F32),
+                          (1000, 3072, 5120, ops.MODE_QKV_ROPE), (900, 3136, 5200, ops.MODE_QKV_ROPE)]:
+        assert k.linear_form(M, N, K, mode) == "pair_256", (M, N, K, mode)
 
 
 class _Norm:
@@ -802,6 +826,8 @@ def test_attention_prefill_tcgen05_at_the_edges_of_tiles_and_windows(head_dim):
     (8, 2, 128, 520, 32, [257], [257], True, True),                        # head size 128: two slabs a query head
     (6, 6, 128, 264, 64, [140, 90], [140, 90], False, True),               # no rotation
     (4, 2, 64, 328, 16, [200], [200], True, False),                        # a layer that reads another layer's cache
+    (16, 4, 128, 5120, 32, [1000], [1000], True, True),                    # a long inner size: pairs of blocks, head size 128
+    (41, 4, 64, 5200, 16, [600, 400], [500, 400], True, True),             # pairs: a partly cached prompt, a tile that N cuts, K's tail
 ])
 def test_linear_qkv_rope_equals_the_projection_followed_by_rope_kv_write(heads, kv_heads, head_dim, hidden, block_size,
                                                                          lengths, new, rotate, write_kv):
