@@ -275,6 +275,47 @@ SKV_EXPORT const char* skv_last_error() { return error_buffer(); }
 SKV_EXPORT int skv_library_dtype() { return SKV_DTYPE; }
 SKV_EXPORT int skv_library_head_dim() { return SKV_HEAD_DIM; }
 
+// Checkpoint tensors in the stored type -> the type a part computes in, on the device (the reference converts
+// FP32 weights to BF16 by dropping the low half, src/cuda/gemm_cuda.cu:74-83; here to nearest even).  Kinds: 0 float32,
+// 1 bfloat16, 2 float16.  The same in every build of the library.
+template <int KIND> struct StoredType;
+template <> struct StoredType<0> { typedef float type; };
+template <> struct StoredType<1> { typedef __nv_bfloat16 type; };
+template <> struct StoredType<2> { typedef __half type; };
+__device__ __forceinline__ float stored_to_float(float v) { return v; }
+__device__ __forceinline__ float stored_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float stored_to_float(__half v) { return __half2float(v); }
+__device__ __forceinline__ void float_to_stored(float v, float* out) { *out = v; }
+__device__ __forceinline__ void float_to_stored(float v, __nv_bfloat16* out) { *out = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void float_to_stored(float v, __half* out) { *out = __float2half_rn(v); }
+
+template <typename From, typename To>
+__global__ void __launch_bounds__(256) convert_kernel(const From* __restrict__ src, To* __restrict__ dst, size_t count) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride)
+        float_to_stored(stored_to_float(src[i]), dst + i);
+}
+
+template <int FROM>
+static int launch_convert(const void* src, void* dst, int to, size_t count, cudaStream_t stream) {
+    typedef typename StoredType<FROM>::type From;
+    const size_t wanted = (count + 255) / 256;
+    const dim3 grid((unsigned)(wanted < 65535 ? wanted : 65535));
+    if (to == 0) convert_kernel<From, float><<<grid, 256, 0, stream>>>((const From*)src, (float*)dst, count);
+    else if (to == 1) convert_kernel<From, __nv_bfloat16><<<grid, 256, 0, stream>>>((const From*)src, (__nv_bfloat16*)dst, count);
+    else convert_kernel<From, __half><<<grid, 256, 0, stream>>>((const From*)src, (__half*)dst, count);
+    const cudaError_t status = cudaGetLastError();
+    return status == cudaSuccess ? 0 : fail("skv_convert", cudaGetErrorString(status));
+}
+
+SKV_EXPORT int skv_convert(const void* src, int from, void* dst, int to, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    if (from < 0 || from > 2 || to < 0 || to > 2) return fail("skv_convert", "types are 0 float32, 1 bfloat16, 2 float16");
+    if (from == 0) return launch_convert<0>(src, dst, to, (size_t)count, stream);
+    if (from == 1) return launch_convert<1>(src, dst, to, (size_t)count, stream);
+    return launch_convert<2>(src, dst, to, (size_t)count, stream);
+}
+
 SKV_EXPORT int skv_embed(const void* table, const int* ids, float* out, int n_tokens, int hidden,
                          int vocab, int* flag, void* scaled, const float* gamma_next, float* partials,
                          int partial_stride, float* row_scale, float eps_next, cudaStream_t stream) {

@@ -96,6 +96,23 @@ class Kernels:
             raise KernelError(f"{name} must be contiguous")
 
     # ---- kernels -------------------------------------------------------------
+    _KINDS = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+    def convert(self, src, out):
+        """out = src in out's type (float32, bfloat16, float16), rounded to nearest even where bits are lost: how
+        checkpoint tensors get from their stored type to the compute type once they are on the device."""
+        if src.dtype not in self._KINDS or out.dtype not in self._KINDS:
+            raise KernelError(f"convert: float32, bfloat16 and float16 only, not {src.dtype} -> {out.dtype}")
+        if src.shape != out.shape or src.device != out.device or not src.is_cuda:
+            raise KernelError("convert: source and result must have one shape and lie on the same GPU")
+        if not (src.is_contiguous() and out.is_contiguous()):
+            raise KernelError("convert: tensors must be contiguous")
+        self.lib.skv_convert.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong,
+                                         ctypes.c_void_p]
+        self._check(self.lib.skv_convert(_ptr(src), self._KINDS[src.dtype], _ptr(out), self._KINDS[out.dtype],
+                                         src.numel(), _stream()), "convert")
+        return out
+
     def embed(self, table, ids, out, flag=None, stats=None):
         """out[t, :] = table[ids[t], :] as float32; with ``stats`` each row's sum of squares too."""
         self._want(table, self.dtype, "table"); self._want(ids, torch.int32, "ids")

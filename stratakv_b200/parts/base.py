@@ -78,7 +78,13 @@ class Runtime:
         """Copy a checkpoint tensor to the device in ``dtype`` (default: the
         compute dtype).  float32 -> bfloat16 rounds to nearest even; the
         reference truncates (``src/cuda/gemm_cuda.cu:74-83``)."""
-        return tensor.to(device=self.device, dtype=dtype or self.dtype).contiguous()
+        target = dtype or self.dtype
+        floats = (torch.float32, torch.bfloat16, torch.float16)
+        if self.device.type == "cuda" and tensor.dtype != target and tensor.dtype in floats and target in floats:
+            # the stored bytes go up as they are and this library's own kernel converts them there
+            stored = tensor.contiguous().to(device=self.device)
+            return self.kernels().convert(stored, torch.empty(stored.shape, dtype=target, device=self.device))
+        return tensor.to(device=self.device, dtype=target).contiguous()
 
     def upload_shared(self, name: str, tensor: torch.Tensor) -> torch.Tensor:
         """``upload`` for a checkpoint tensor that several parts may name (tied embedding and head):

@@ -34,6 +34,30 @@ def test_embed(dtype, vocab, hidden, n):
     assert torch.equal(out, table[ids.long()].float())
 
 
+@pytest.mark.parametrize("build", DTYPES)
+def test_convert_rounds_to_nearest_even(build):
+    """Checkpoint tensors are converted on the device by the library's own kernel (the reference drops the low
+    half of an FP32 weight, src/cuda/gemm_cuda.cu:74-83; this rounds to nearest even, as torch does)."""
+    k = lib(build)
+    generator = torch.Generator(device="cuda").manual_seed(3)
+    values = torch.randn(100003, device="cuda", generator=generator) * 3
+    # ties of the bfloat16 grid (the 16 bits below are exactly half), both parities, and special values
+    ties = (torch.tensor([0x3F808000, 0x3F818000, 0xBF808000, 0x7F7F8000, 0x00008000, 0x00000001], dtype=torch.int64)
+            .to(torch.int32).view(torch.float32).cuda())
+    special = torch.tensor([0.0, -0.0, float("inf"), float("-inf"), 65504.0, 70000.0, 1e-8, 3.4e38], device="cuda")
+    source = torch.cat([values, ties, special])
+    for src_dtype in (torch.float32, torch.float16, torch.bfloat16):
+        stored = source.to(src_dtype)
+        for dst_dtype in (torch.float32, torch.bfloat16, torch.float16):
+            out = torch.full(stored.shape, 7.0, dtype=dst_dtype, device="cuda")
+            k.convert(stored, out)
+            assert torch.equal(out, stored.to(dst_dtype)), (src_dtype, dst_dtype)
+    nan = torch.tensor([float("nan")], device="cuda")
+    assert torch.isnan(k.convert(nan, torch.zeros(1, dtype=torch.bfloat16, device="cuda"))).all()
+    with pytest.raises(Exception, match="float32, bfloat16 and float16 only"):
+        k.convert(torch.zeros(4, dtype=torch.int32, device="cuda"), torch.zeros(4, device="cuda"))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,hidden,eps", [(5, 80, 1e-5), (3, 2048, 1e-6), (9, 1000, 3e-3), (100, 264, 1e-5),
                                              (70, 2048, 1e-6), (65, 82, 1e-5)])
