@@ -126,6 +126,13 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint
         : "memory");
 }
 
+// One lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(chosen));
+    return chosen != 0;
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -143,12 +150,17 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) 
         : "memory");
 }
 
-// silu(g) = g / (1 + e^-g), the form of the reference's GPU kernel (src/cuda/gemm_cuda.cu:229).
-// For very negative g the exponential overflows to infinity and the quotient is -0, the right limit.
-__device__ __forceinline__ float silu_gate(float g) { return g / (1.0f + expf(-g)); }
-
-// The gate's activation, chosen by the caller (common.cuh names them).
-__device__ __forceinline__ float gate_activation(float g, int act) { return act == ACT_GELU_TANH ? gelu_tanh(g) : silu_gate(g); }
+// The gate's activation, chosen by the caller (common.cuh names them), as g * sigmoid(z) = g / (1 + e^-z): z = g for
+// silu (the form of the reference's GPU kernel, src/cuda/gemm_cuda.cu:229), z = 2 sqrt(2/pi) (g + 0.044715 g^3) for the
+// tanh form of gelu (g/2 (1 + tanh(z/2))).  Exponential and quotient are the special-function unit's (`ex2.approx`
+// on z log2 e, `rcp.approx`): a few units in the last place of a float (2 + |1.16 z| for the exponential), far
+// below the bfloat16 the product is rounded to.  With libm's expf and an IEEE division the gated epilogue of a
+// 256-column tile took longer than the tile's main loop (2,048 x 11,264 x 2,048: 76.7 us against 63.8 us).  Past
+// z = -88 the exponential overflows to infinity and the quotient is -0, the right limit.
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    const float z = act == ACT_GELU_TANH ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+    return __fdividef(g, 1.0f + __expf(-z));
+}
 
 // The epilogue of one output tile for one of the four epilogue warps: reads the warp's quarter of the
 // accumulator (TMEM lanes 32*quarter .., one output row per thread) and stores it in the mode asked for.
@@ -449,8 +461,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     // A block walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...; neighbouring tiles share their
     // W rows (m runs fastest), so blocks that run together read the same W tile from L2.
-    if (warp == 0 && lane == 0) {
-        // ---- loader -------------------------------------------------------------------------
+    if (warp == 0) {
+        // ---- loader: the whole warp walks the loop, one elected lane issues ------------------------
         bool ok = true;
         int it = 0;                               // k iterations issued so far, over all tiles
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -459,18 +471,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int s = it % STAGES;
                 if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, flag);
                 if (!ok) break;
-                const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, i * TC_BK, m0, full0 + 8 * s);
-                tma_load_2d(a_dst + A_BYTES, &map_w, i * TC_BK, n0, full0 + 8 * s);
+                if (elect_one()) {
+                    const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, i * TC_BK, m0, full0 + 8 * s);
+                    tma_load_2d(a_dst + A_BYTES, &map_w, i * TC_BK, n0, full0 + 8 * s);
+                }
+                __syncwarp();
             }
         }
         if (!ok) {
             // let the copies in flight land before the block leaves (bounded)
             for (int i = max(0, it - STAGES); i < it; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr);
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- tensor-core issue ------------------------------------------------------------------
+    } else if (warp == 1) {
+        // ---- tensor-core issue: the whole warp walks the loop, one elected lane issues ----------------
         constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
         bool ok = true;
         int it = 0, local = 0;
@@ -487,16 +502,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-                const uint64_t a_desc = umma_desc(a_addr), w_desc = umma_desc(a_addr + A_BYTES);
+                if (elect_one()) {
+                    const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                    const uint64_t a_desc = umma_desc(a_addr), w_desc = umma_desc(a_addr + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k) {
-                    // 16 bfloat16 = 32 bytes further along K: +2 in the descriptor's 16-byte units
-                    umma_bf16(acc, a_desc + 2 * k, w_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        // 16 bfloat16 = 32 bytes further along K: +2 in the descriptor's 16-byte units
+                        umma_bf16(acc, a_desc + 2 * k, w_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
                 }
-                umma_commit(empty0 + 8 * s);      // frees the stage when these MMAs have read it
+                __syncwarp();
             }
-            if (ok) umma_commit(acc_full0 + 8 * buf);   // arrives when every MMA of the tile has finished
+            if (ok && elect_one()) umma_commit(acc_full0 + 8 * buf);   // arrives when every MMA of the tile has finished
+            __syncwarp();
         }
     } else if (warp >= 2) {
         // ---- epilogue ---------------------------------------------------------------------------
@@ -627,8 +646,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
 
-    if (warp == 0 && lane == 0) {
-        // ---- loader: this block's rows of A and its half of the W rows ------------------------------
+    if (warp == 0) {
+        // ---- loader: this block's rows of A and its half of the W rows (the warp walks, an elected lane issues) ----
         bool ok = true;
         int it = 0;
         const uint32_t first_full0 = cluster_address(full0, 0);
@@ -639,10 +658,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const int s = it % STAGES;
                 if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, flag);
                 if (!ok) break;
-                const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-                if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
-                tma_load_2d_pair(a_dst, &map_a, i * TC_BK, m0, first_full0 + 8 * s);
-                tma_load_2d_pair(a_dst + A_BYTES, &map_w, i * TC_BK, w0, first_full0 + 8 * s);
+                if (elect_one()) {
+                    const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                    tma_load_2d_pair(a_dst, &map_a, i * TC_BK, m0, first_full0 + 8 * s);
+                    tma_load_2d_pair(a_dst + A_BYTES, &map_w, i * TC_BK, w0, first_full0 + 8 * s);
+                }
+                __syncwarp();
             }
         }
         if (!ok && rank == 0) {
@@ -650,8 +672,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             // one at the cluster barrier below
             for (int i = max(0, it - STAGES); i < it; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr);
         }
-    } else if (warp == 1 && lane == 0 && rank == 0) {
-        // ---- tensor-core issue, for both blocks -------------------------------------------------------
+    } else if (warp == 1 && rank == 0) {
+        // ---- tensor-core issue, for both blocks: the warp walks the loop, one elected lane issues -----
         constexpr uint32_t idesc = umma_idesc(2 * TC_BM, BN);
         bool ok = true;
         int it = 0, local = 0;
@@ -668,14 +690,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-                const uint64_t a_desc = umma_desc(a_addr), w_desc = umma_desc(a_addr + A_BYTES);
+                if (elect_one()) {
+                    const uint32_t a_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                    const uint64_t a_desc = umma_desc(a_addr), w_desc = umma_desc(a_addr + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)
-                    umma_bf16_pair(acc, a_desc + 2 * k, w_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit_pair(empty0 + 8 * s);
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16_pair(acc, a_desc + 2 * k, w_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(empty0 + 8 * s);
+                }
+                __syncwarp();
             }
-            if (ok) umma_commit_pair(acc_full0 + 8 * buf);
+            if (ok && elect_one()) umma_commit_pair(acc_full0 + 8 * buf);
+            __syncwarp();
         }
     } else if (warp >= 2) {
         // ---- epilogue: this block's 128 rows of the tile ------------------------------------------
@@ -786,8 +812,10 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
         if (!ok) {
             for (int i = max(0, k_iters - STAGES); i < k_iters; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr);
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- tensor-core issue ------------------------------------------------------------------------
+    } else if (warp == 1) {
+        // ---- tensor-core issue: the warp walks the loop whole and one elected lane issues (a lone lane under
+        // `lane == 0` took about 95 cycles per tcgen05 instruction in the prefill attention kernel, an elected
+        // lane of a converged warp 70; with eight small stages a block that chain is on the kernel's path) -------
         constexpr uint32_t idesc = umma_idesc(128, MP);
         bool ok = true;
         for (int i = 0; i < k_iters && ok; ++i) {
@@ -795,14 +823,18 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
             ok = mbar_wait(full0 + 8 * s, (i / STAGES) & 1, flag);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t w_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-            const uint64_t w_desc = umma_desc(w_addr), x_desc = umma_desc(w_addr + W_BYTES);
+            if (elect_one()) {
+                const uint32_t w_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
+                const uint64_t w_desc = umma_desc(w_addr), x_desc = umma_desc(w_addr + W_BYTES);
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; ++k)
-                umma_bf16(tmem_base, w_desc + 2 * k, x_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-            umma_commit(empty0 + 8 * s);
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    umma_bf16(tmem_base, w_desc + 2 * k, x_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);
+            }
+            __syncwarp();
         }
-        if (ok) umma_commit(acc_full);            // arrives when every MMA has finished (at once if there were none)
+        if (ok && elect_one()) umma_commit(acc_full);   // arrives when every MMA has finished (at once if there were none)
+        __syncwarp();
     }
     // ---- epilogue: warps 2-5, one weight row per thread -----------------------------------------------
     const int quarter = warp & 3;
@@ -1154,6 +1186,9 @@ static int launch_few_tokens(const void* a, const void* w, void* out, int M, int
 // other modes do not).
 enum { FORM_FEW_TOKENS = 0, FORM_128 = 1, FORM_160 = 2, FORM_256 = 3, FORM_PAIR = 4 };
 
+// (Tried: a width of 192 for the bfloat16 store and, at head size 64, the rotary epilogue.  The q|k|v projection of
+// 2,048 tokens x 2,560 columns, 224 tiles of 192 instead of 160 of 256, took 29.5 us against 27.8 with the rotary
+// epilogue, whose work per tile does not shrink with the width; the prefill did not move.)
 static int choose_form(int M, int N, int K, int mode) {
     if (M <= 128) return FORM_FEW_TOKENS;
     const long long m_tiles = (M + 127) / 128;

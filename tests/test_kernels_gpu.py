@@ -158,7 +158,8 @@ def _products(a, w, chunk=512):
 @pytest.mark.parametrize("M,N,K,modes", [
     (129, 2048, 2048, "store_f32 store add"),        # 128-wide tiles, one tile per block, a tail of one row
     (300, 2560, 2048, "store_f32 store add"),        # the q|k|v projection of a short prompt
-    (2048, 2560, 2048, "store_f32 add"),             # 256-wide tiles: 160 tiles on 148 blocks
+    (2048, 2560, 2048, "store_f32 add store"),       # 160-wide tiles for the float epilogues, 256-wide for bfloat16 (160 tiles on 148 blocks)
+    (2048, 11264, 520, "gated"),                     # 256-wide tiles: 704 of them, five a block, a short inner size
     (2048, 2048, 5632, "store add"),                 # the down projection: 88 steps of K
     (4096, 2048, 5632, "add"),                       # 256 tiles, residual sum through the copy engine
     (2048, 11264, 2048, "gated"),                    # gate and up: 704 tiles, almost five per block
@@ -224,6 +225,7 @@ def test_the_shapes_of_these_tests_reach_every_tensor_memory_kernel():
     assert k.linear_form(2048, 2500, 2048, ops.MODE_ADD_F32) == "tile_160"
     assert k.linear_form(2048, 2560, 2048, ops.MODE_STORE) == "tile_256"
     assert k.linear_form(2048, 2560, 2048, ops.MODE_QKV_ROPE) == "tile_256"
+    assert k.linear_form(2048, 11264, 520, ops.MODE_GATED) == "tile_256"            # a short inner size: no pair
     assert k.linear_form(2048, 2048, 2048, ops.MODE_ADD_F32) == "tile_256"      # one short tile a block: no pair
     for M, N, K, mode in [(2048, 11264, 2048, ops.MODE_GATED), (2048, 2048, 5632, ops.MODE_ADD_F32),
                           (1000, 4112, 5200, ops.MODE_GATED), (1000, 4112, 5200, ops.MODE_STORE),
@@ -850,6 +852,7 @@ def test_attention_prefill_tcgen05_at_the_edges_of_tiles_and_windows(head_dim):
     (8, 2, 128, 520, 32, [257], [257], True, True),                        # head size 128: two slabs a query head
     (6, 6, 128, 264, 64, [140, 90], [140, 90], False, True),               # no rotation
     (4, 2, 64, 328, 16, [200], [200], True, False),                        # a layer that reads another layer's cache
+    (32, 4, 64, 2048, 64, [2041], [2041], True, True),                     # the TinyLlama layer on a long prompt: 160 tiles on 148 blocks
     (16, 4, 128, 5120, 32, [1000], [1000], True, True),                    # a long inner size: pairs of blocks, head size 128
     (41, 4, 64, 5200, 16, [600, 400], [500, 400], True, True),             # pairs: a partly cached prompt, a tile that N cuts, K's tail
 ])
