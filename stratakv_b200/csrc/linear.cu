@@ -351,11 +351,13 @@ static int launch_skinny_as(const void* a, const void* w, void* out, int M, int 
                       mode, act, norm);
 }
 
-// Warps per block.  Many row tiles (>= 4 per SM): 4 warps, compiled to fit 5 blocks on an SM so that
-// e.g. 704 tiles run as one wave.  Few row tiles: 8 warps (two blocks fit on an SM, so the next
-// kernel's weight loads overlap this one's end), or 16 when the inner size is so long that 8 warps
-// would need more than two rounds of loads each and the tiles are no more than the SMs (a block of 16 warps
-// has an SM to itself; 256 tiles of 8 warps run as one wave, of 16 warps as two).  Never more warps than k steps.
+// Warps per block.  Four to five row tiles per SM: 4 warps, compiled to fit 5 blocks on an SM so that
+// e.g. 704 tiles run as one wave.  Fewer row tiles, or more than one such wave holds: 8 warps (two blocks fit on an
+// SM, so the next kernel's weight loads overlap this one's end; with many tiles, blocks of 8 warps that come and go
+// keep the memory pipe fuller than two waves of 4-warp blocks: 22,016 x 4,096 at 8 tokens 44.2 -> 35.9 us, 32,000 x
+// 2,048 31.6 -> 28.3 us), or 16 when the inner size is so long that 8 warps would need more than two rounds of loads
+// each and the tiles are no more than the SMs (a block of 16 warps has an SM to itself; 256 tiles of 8 warps run as
+// one wave, of 16 warps as two).  Never more warps than k steps.
 template <int TG, int U, int MAX_WARPS>
 static int launch_skinny(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                          const NormArgs& norm, cudaStream_t stream) {
@@ -363,11 +365,9 @@ static int launch_skinny(const void* a, const void* w, void* out, int M, int N, 
     const int steps = (K + 31) / 32;
     const long long blocks = (long long)row_tiles * chunks;
     const int sms = sm_count();
-    int warps = blocks >= sms * 4 ? 4 : 8;
-    // A few more tiles than five blocks of 4 warps per SM hold (768 at hidden size 4096) would leave a second,
-    // nearly empty wave that doubles the time; blocks of 3 warps (96 registers a thread) fit 7 to an SM.  (Blocks
-    // of 2 warps or 1, of which 10 or 21 fit, measured slower than two waves.)
-    if (TG <= 2 && blocks > sms * 5 && blocks <= sms * 7) warps = 3;
+    int warps = (blocks >= sms * 4 && blocks <= sms * 5) ? 4 : 8;
+    // (Blocks of 3 warps, of which 7 fit on an SM, were once used for a few more tiles than five blocks of 4 warps per SM
+    // hold, 768 at hidden size 4096; blocks of 8 warps measured faster there too: 12,288 x 4,096 at 8 tokens 27.9 -> 22.5 us.)
     if (warps == 8 && MAX_WARPS >= 16 && steps > 8 * U * 2 && blocks <= sms) warps = 16;   // (16 warps: one block per SM)
     if (warps > MAX_WARPS) warps = MAX_WARPS;
     while (warps > 1 && warps > steps) warps >>= 1;
