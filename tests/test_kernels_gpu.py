@@ -87,7 +87,9 @@ def pack_gate_up(w):
 @pytest.mark.parametrize("M,N,K", [(1, 48, 64), (3, 331, 80), (8, 256, 2048), (9, 100, 264), (17, 96, 96),
                                    (33, 80, 176), (64, 512, 512), (70, 130, 520), (200, 64, 72),
                                    (32, 2048, 5632), (64, 2560, 2048), (100, 1000, 1032), (128, 384, 4096),
-                                   (5, 12288, 264)])          # 768 row tiles: blocks of 3 warps
+                                   (5, 12288, 264),           # 768 row tiles of the small-step kernel
+                                   (20, 19000, 136), (64, 19072, 520), (100, 20000, 264)])   # more 128-row tiles than
+                                                              # SMs: the swapped kernel's shallow rings, two blocks an SM
 def test_linear_store_and_add(dtype, M, N, K):
     from stratakv_b200 import ops
     k = lib(dtype)
@@ -112,7 +114,7 @@ def test_linear_store_and_add(dtype, M, N, K):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,F,K", [(1, 176, 64), (5, 104, 80), (8, 5632, 2048), (40, 256, 96), (130, 24, 72),
-                                   (24, 72, 264), (64, 5632, 2048), (128, 200, 520)])
+                                   (24, 72, 264), (64, 5632, 2048), (128, 200, 520), (48, 9600, 200)])   # (the last: shallow rings)
 @pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
 def test_linear_gated(dtype, M, F, K, activation):
     """``act(gate) * up`` in the epilogue of one projection, for every activation the kernels name (the
