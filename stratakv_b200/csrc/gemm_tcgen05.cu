@@ -81,6 +81,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
@@ -601,6 +608,10 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                  ::"r"(bar), "h"(both) : "memory");
 }
 
+// (Tried: stages of two chunks of 64 columns, each operand brought by one copy of 32 KB through a three-dimensional
+// tensor map as in the few-token kernel below, three stages.  The layer shapes did not move, 65.7 against 66.5 us for
+// 2,048 x 11,264 x 2,048; 8,192 cubed went from 799 to 760 us.  Copies from L2 come back soon enough for three of 16 KB
+// on their way to feed the tensor pipe.)
 template <int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -755,12 +766,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 // row's results for 32 tokens at a time, and the 32 lanes of a warp write 32 neighbouring columns of a
 // token's output row.  With splits > 1 the blocks of a cluster each take a part of K; the others push their
 // accumulators into the first block's shared memory, which adds them in rank order.
-template <int MP, int STAGES>
+// A stage holds CH chunks of 64 columns.  With CH = 2 one copy brings both chunks of the weight rows (and one those of the
+// tokens): the tensor maps are then three-dimensional, [64][rows][K / 64] with the chunk index as the slowest dimension of
+// the box, and the box lands as CH tiles of rows x 64, one behind the other.  An SM keeps only about three copies on their
+// way whatever their size, so copies of 16 KB stream 45 GB/s into a block and copies of 32 KB 65 (88 blocks: 3.6
+// against 4.5 TB/s over the GPU).  That form needs K to be a multiple of 64 (a chunk that K cuts would continue into the
+// next row); other K take CH = 1 with the two-dimensional maps, which fill the tail with zeros.
+template <int MP, int STAGES, int CH>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                                void* __restrict__ out, int M, int N, int K, int mode, int act, int splits,
                                int* __restrict__ flag) {
-    constexpr uint32_t W_BYTES = 128 * TC_BK * 2, X_BYTES = MP * TC_BK * 2, STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t W_CHUNK = 128 * TC_BK * 2, X_CHUNK = MP * TC_BK * 2;
+    constexpr uint32_t W_BYTES = W_CHUNK * CH, X_BYTES = X_CHUNK * CH, STAGE_BYTES = W_BYTES + X_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(tiles + (size_t)STAGES * STAGE_BYTES);      // full[STAGES], empty[STAGES], acc_full
@@ -770,8 +788,17 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const int split = blockIdx.y;                                           // == rank in the cluster
     const int k_blocks = (K + TC_BK - 1) / TC_BK;
     const int per_split = (k_blocks + splits - 1) / splits;
-    const int k_first = split * per_split, k_iters = max(0, min(k_blocks, k_first + per_split) - k_first);
+    const int k_first = split * per_split, my_chunks = max(0, min(k_blocks, k_first + per_split) - k_first);
+    const int k_iters = (my_chunks + CH - 1) / CH;                          // stages of CH chunks (the last may hold fewer)
     const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES), acc_full = smem_addr(bars + 2 * STAGES);
+    auto load_w = [&](uint32_t dst, int i, uint32_t bar) {
+        if (CH == 1) tma_load_2d(dst, &map_w, (k_first + i) * TC_BK, n0, bar);
+        else tma_load_3d(dst, &map_w, 0, n0, k_first + i * CH, bar);
+    };
+    auto load_x = [&](uint32_t dst, int i, uint32_t bar) {
+        if (CH == 1) tma_load_2d(dst, &map_x, (k_first + i) * TC_BK, 0, bar);
+        else tma_load_3d(dst, &map_x, 0, 0, k_first + i * CH, bar);
+    };
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
@@ -795,19 +822,18 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
         const int ahead = min(STAGES, k_iters);
         for (int i = 0; i < ahead; ++i) {
             mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
-            tma_load_2d(smem_addr(tiles + (size_t)i * STAGE_BYTES), &map_w, (k_first + i) * TC_BK, n0, full0 + 8 * i);
+            load_w(smem_addr(tiles + (size_t)i * STAGE_BYTES), i, full0 + 8 * i);
         }
         pdl_wait();
-        for (int i = 0; i < ahead; ++i)
-            tma_load_2d(smem_addr(tiles + (size_t)i * STAGE_BYTES) + W_BYTES, &map_x, (k_first + i) * TC_BK, 0, full0 + 8 * i);
+        for (int i = 0; i < ahead; ++i) load_x(smem_addr(tiles + (size_t)i * STAGE_BYTES) + W_BYTES, i, full0 + 8 * i);
         for (int i = ahead; i < k_iters && ok; ++i) {
             const int s = i % STAGES;
             ok = mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, flag);
             if (!ok) break;
             const uint32_t dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
             mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-            tma_load_2d(dst, &map_w, (k_first + i) * TC_BK, n0, full0 + 8 * s);
-            tma_load_2d(dst + W_BYTES, &map_x, (k_first + i) * TC_BK, 0, full0 + 8 * s);
+            load_w(dst, i, full0 + 8 * s);
+            load_x(dst + W_BYTES, i, full0 + 8 * s);
         }
         if (!ok) {
             for (int i = max(0, k_iters - STAGES); i < k_iters; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, nullptr);
@@ -825,10 +851,16 @@ gemm_tcgen05_few_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const 
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (elect_one()) {
                 const uint32_t w_addr = smem_addr(tiles + (size_t)s * STAGE_BYTES);
-                const uint64_t w_desc = umma_desc(w_addr), x_desc = umma_desc(w_addr + W_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)
-                    umma_bf16(tmem_base, w_desc + 2 * k, x_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                for (int c = 0; c < CH; ++c) {
+                    // (a stage's second chunk may lie past this block's part of K: it was copied, it is not used)
+                    if (i * CH + c < my_chunks) {
+                        const uint64_t w_desc = umma_desc(w_addr + c * W_CHUNK), x_desc = umma_desc(w_addr + W_BYTES + c * X_CHUNK);
+#pragma unroll
+                        for (int k = 0; k < TC_BK / 16; ++k)
+                            umma_bf16(tmem_base, w_desc + 2 * k, x_desc + 2 * k, idesc, (i > 0 || c > 0 || k > 0) ? 1u : 0u);
+                    }
+                }
                 umma_commit(empty0 + 8 * s);
             }
             __syncwarp();
@@ -1004,6 +1036,37 @@ static int tensor_map(const void* base, int rows, int cols, int elem_bytes, int 
     return 0;
 }
 
+// A bfloat16 matrix [rows, K], K a multiple of 64, seen as [64][rows][K / 64]: a box of 64 x box_rows x chunks brings
+// `chunks` neighbouring tiles of box_rows x 64 in one copy, tile after tile in shared memory (each 128-byte swizzled as
+// the two-dimensional map leaves it).  Rows past the matrix and chunks past K are filled with zeros.
+static int tensor_map_chunks(const void* base, int rows, int K, int box_rows, int chunks, CUtensorMap* out) {
+    static std::mutex lock;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{base, rows, K, box_rows, -chunks, 2};
+    std::lock_guard<std::mutex> guard(lock);
+    auto found = cache.find(key);
+    if (found != cache.end()) { *out = found->second; return 0; }
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return fail("skv_linear(tcgen05)", "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {(cuuint64_t)TC_BK, (cuuint64_t)rows, (cuuint64_t)(K / TC_BK)};
+    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)TC_BK * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows, (cuuint32_t)chunks};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap map;
+    const CUresult status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS) {
+        char detail[64];
+        snprintf(detail, sizeof detail, "cuTensorMapEncodeTiled (chunks) failed with code %d", (int)status);
+        return fail("skv_linear(tcgen05)", detail);
+    }
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, map);
+    *out = map;
+    return 0;
+}
+
 static int tc_sm_count() { return sm_count(); }
 
 template <int BN, int STAGES>
@@ -1130,13 +1193,19 @@ static double pair_cost(int M, int N, int K) {
     return (double)rounds * 256 / 1.04;
 }
 
-template <int MP, int STAGES>
+template <int MP, int STAGES, int CH>
 static int launch_few_tokens(const void* a, const void* w, void* out, int M, int N, int K, int mode, int act,
                              int* flag, cudaStream_t stream) {
     CUtensorMap map_w, map_x;
-    if (int code = tensor_map(w, N, K, 2, 128, TC_BK, &map_w)) return code;
-    if (int code = tensor_map(a, M, K, 2, MP, TC_BK, &map_x)) return code;
-    constexpr size_t ring = (size_t)STAGES * (128 * TC_BK * 2 + MP * TC_BK * 2);
+    if (CH == 1) {
+        if (int code = tensor_map(w, N, K, 2, 128, TC_BK, &map_w)) return code;
+        if (int code = tensor_map(a, M, K, 2, MP, TC_BK, &map_x)) return code;
+    } else {
+        if (K % TC_BK != 0) return fail("skv_linear(tcgen05)", "copies of several chunks need an inner size that is a multiple of 64");
+        if (int code = tensor_map_chunks(w, N, K, 128, CH, &map_w)) return code;
+        if (int code = tensor_map_chunks(a, M, K, MP, CH, &map_x)) return code;
+    }
+    constexpr size_t ring = (size_t)STAGES * CH * (128 * TC_BK * 2 + MP * TC_BK * 2);
     constexpr size_t smem = ring + (2 * STAGES + 1) * 8 + 16 + 1024;
     static int sm_count = 0;
     if (sm_count == 0) {
@@ -1144,7 +1213,7 @@ static int launch_few_tokens(const void* a, const void* w, void* out, int M, int
         if (cudaGetDevice(&device) != cudaSuccess ||
             cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
             return fail("skv_linear(tcgen05)", "cannot read the number of SMs");
-        cudaError_t status = cudaFuncSetAttribute(gemm_tcgen05_few_tokens_kernel<MP, STAGES>,
+        cudaError_t status = cudaFuncSetAttribute(gemm_tcgen05_few_tokens_kernel<MP, STAGES, CH>,
                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("skv_linear(tcgen05)", cudaGetErrorString(status));
         sm_count = count;
@@ -1171,7 +1240,7 @@ static int launch_few_tokens(const void* a, const void* w, void* out, int M, int
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pdl_enabled() ? 2 : 1;
-    const cudaError_t status = cudaLaunchKernelEx(&config, gemm_tcgen05_few_tokens_kernel<MP, STAGES>, map_w, map_x, out,
+    const cudaError_t status = cudaLaunchKernelEx(&config, gemm_tcgen05_few_tokens_kernel<MP, STAGES, CH>, map_w, map_x, out,
                                                   M, N, K, mode, act, splits, flag);
     if (status != cudaSuccess) return fail("skv_linear(tcgen05)", cudaGetErrorString(status));
     return 0;
@@ -1215,12 +1284,18 @@ int linear_tcgen05(const void* a, const void* w, void* out, int M, int N, int K,
     // 32,000 x 2,048: 26.3 -> 23.4).  With fewer tiles the deep ring of a block alone on its SM is faster (2,048 x
     // 5,632: 10.0 against 12.6 us).
     const bool many_tiles = (N + 127) / 128 > tc_sm_count();
-    if (M <= 32) return many_tiles ? launch_few_tokens<32, 4>(a, w, out, M, N, K, mode, act, flag, stream)
-                                   : launch_few_tokens<32, 8>(a, w, out, M, N, K, mode, act, flag, stream);
-    if (M <= 64) return many_tiles ? launch_few_tokens<64, 4>(a, w, out, M, N, K, mode, act, flag, stream)
-                                   : launch_few_tokens<64, 8>(a, w, out, M, N, K, mode, act, flag, stream);
-    if (M <= 128) return many_tiles ? launch_few_tokens<128, 3>(a, w, out, M, N, K, mode, act, flag, stream)
-                                    : launch_few_tokens<128, 6>(a, w, out, M, N, K, mode, act, flag, stream);
+    // (copies of two chunks where K allows it and the blocks are few enough for each to be limited by what it can keep
+    // on its way; see the kernel)
+    const bool two_chunks = K % TC_BK == 0 && !many_tiles;
+    if (M <= 32) return many_tiles ? launch_few_tokens<32, 4, 1>(a, w, out, M, N, K, mode, act, flag, stream)
+                       : two_chunks ? launch_few_tokens<32, 4, 2>(a, w, out, M, N, K, mode, act, flag, stream)
+                                    : launch_few_tokens<32, 8, 1>(a, w, out, M, N, K, mode, act, flag, stream);
+    if (M <= 64) return many_tiles ? launch_few_tokens<64, 4, 1>(a, w, out, M, N, K, mode, act, flag, stream)
+                       : two_chunks ? launch_few_tokens<64, 4, 2>(a, w, out, M, N, K, mode, act, flag, stream)
+                                    : launch_few_tokens<64, 8, 1>(a, w, out, M, N, K, mode, act, flag, stream);
+    if (M <= 128) return many_tiles ? launch_few_tokens<128, 3, 1>(a, w, out, M, N, K, mode, act, flag, stream)
+                        : two_chunks ? launch_few_tokens<128, 3, 2>(a, w, out, M, N, K, mode, act, flag, stream)
+                                     : launch_few_tokens<128, 6, 1>(a, w, out, M, N, K, mode, act, flag, stream);
     switch (choose_form(M, N, K, mode)) {
         case FORM_PAIR: return launch_pair(a, w, out, M, N, K, mode, act, flag, stream);
         case FORM_160: return launch_tc<160, 5>(a, w, out, M, N, K, mode, act, flag, stream);
