@@ -118,7 +118,7 @@ def _compile(nvcc: str, dtype: str, head_dim: int, target: Path, verbose: bool) 
     done = threading.Event()
 
     def heartbeat():
-        while not done.wait(10.0):
+        while not done.wait(5.0):
             say(f"still compiling ({time.time() - start:.0f} s)")
 
     ticker = threading.Thread(target=heartbeat, daemon=True)
