@@ -55,7 +55,12 @@ def _token_array(tokens) -> np.ndarray:
             pass                                 # (numpy integers, or something that is no token id: the slow way tells)
     out = np.asarray(tokens)
     if out.dtype.kind not in "iu":
-        out = np.array([int(t) for t in tokens], dtype=np.int64)
+        if out.dtype.kind == "b" or not all(isinstance(t, (int, np.integer)) for t in tokens):
+            raise StepError("token ids must be integers")
+        try:
+            out = np.array([int(t) for t in tokens], dtype=np.int64)
+        except OverflowError:
+            raise StepError("a token id is outside the vocabulary (it does not even fit 64 bits)") from None
     return out
 
 

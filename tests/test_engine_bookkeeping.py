@@ -57,6 +57,15 @@ def test_step_checks(tmp_path):
         engine.step([StepEntry(slot, [1, 256], [0])])
     with pytest.raises(StepError, match="wanted place"):
         engine.step([StepEntry(slot, [1, 2], [2])])
+    import numpy as np
+    for not_ids in ([1.5, 2], ["3"], [1, 2 ** 70], np.array([True, False])):
+        with pytest.raises(StepError, match="integers|outside the vocabulary"):
+            engine.step([StepEntry(slot, not_ids, [0])])
+    # token ids may come as a list, a tuple, numpy integers or an integer array
+    for ids in ((1, 2), [np.int64(1), np.int32(2)], np.array([1, 2], dtype=np.int32), np.array([1, 2], dtype=np.uint8)):
+        probe = engine.open_sequence()
+        assert engine.step([StepEntry(probe, ids, [1])]).shape == (1, 256)
+        engine.close_sequence(probe)
     with pytest.raises(StepError, match="at least one token"):
         engine.step([StepEntry(slot, [], [])])
     with pytest.raises(StepError, match="twice"):
