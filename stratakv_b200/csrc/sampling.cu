@@ -97,8 +97,10 @@ __device__ __forceinline__ unsigned long long sort_key(float v, int index) {
 }
 
 __device__ __forceinline__ unsigned long long fixed_mass(float v, float max_value) {
-    // exp(v - max) in (0, 1] as 40-bit fixed point; never below 1 so that every kept token can be drawn
-    const float w = expf(v - max_value);
+    // exp(v - max) in (0, 1] as 40-bit fixed point; never below 1 so that every kept token can be drawn.  (The
+    // special-function unit's exponential, a few units in the last place of a float off libm's: a row is walked up to
+    // twenty times and libm's expf was most of each walk.  Whatever it returns, every pass sees the same masses.)
+    const float w = __expf(v - max_value);
     const unsigned long long q = (unsigned long long)(w * 1099511627776.0f);     // exact: a power of two
     return q ? q : 1ull;
 }
@@ -122,51 +124,119 @@ __device__ __forceinline__ uint32_t philox_first_word(unsigned long long seed, u
 }
 
 constexpr int SAMPLE_THREADS = 512;
+constexpr int SAMPLE_WARPS = SAMPLE_THREADS / 32;
+
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    return v;
+}
 
 // Finds, among elements with key >= floor_key, the key where the running total of
 // `what` (walking keys downward) first reaches `target`.  COUNT: what = 1 per
 // element; otherwise what = fixed_mass.  Returns the key (every thread).
+// The histogram of a pass is filled a warp at a time: lanes whose elements fall in the same bin (most of a row does
+// in the passes over the exponent bits) add up among themselves first and one of them adds to shared memory (every
+// element for itself meant tens of thousands of atomic additions to three or four addresses a pass).  Masses are
+// integers below 2^41, added as two halves of 20 bits so that the warp's 32-bit reduction serves.  When all 32 bits
+// of the value are fixed and one element alone has that value there is no tie for the index bits to break: the last
+// four passes are left out and the key's index bits stay zero, which keeps the same elements.
 template <bool COUNT>
 __device__ unsigned long long radix_select(const float* __restrict__ row, int vocab, float inv_scale_div,
                                            float max_value, unsigned long long floor_key,
-                                           unsigned long long target, unsigned long long* hist,
+                                           unsigned long long target, unsigned long long* hist, unsigned int* members,
                                            unsigned long long* shared_pick) {
+    const int lane = threadIdx.x & 31;
     unsigned long long prefix = 0ull, remaining = target;
     for (int shift = 56; shift >= 0; shift -= 8) {
-        for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) { hist[b] = 0ull; members[b] = 0u; }
         __syncthreads();
         const unsigned long long high_mask = shift == 56 ? 0ull : (~0ull << (shift + 8));
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const float v = row[i] / inv_scale_div;
-            const unsigned long long key = sort_key(v, i);
-            if (key < floor_key || (key & high_mask) != prefix) continue;
-            const int bin = (int)((key >> shift) & 0xFFull);
-            atomicAdd(&hist[bin], COUNT ? 1ull : fixed_mass(v, max_value));
+        for (int base4 = (int)threadIdx.x - lane; base4 < vocab; base4 += 4 * SAMPLE_THREADS) {   // the same trips for a warp's lanes
+          float x[4];                                                    // four loads on their way
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+              const int i = base4 + u * SAMPLE_THREADS + lane;
+              x[u] = i < vocab ? row[i] : 0.0f;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int base = base4 + u * SAMPLE_THREADS;
+            if (base >= vocab) break;
+            const int i = base + lane;
+            bool valid = false;
+            int bin = 0;
+            unsigned long long mass = 0ull;
+            if (i < vocab) {
+                const float v = x[u] / inv_scale_div;
+                const unsigned long long key = sort_key(v, i);
+                valid = key >= floor_key && (key & high_mask) == prefix;
+                bin = (int)((key >> shift) & 0xFFull);
+                if (!COUNT && valid) mass = fixed_mass(v, max_value);
+            }
+            const unsigned int voters = __ballot_sync(0xffffffffu, valid);
+            if (valid) {
+                const unsigned int peers = __match_any_sync(voters, bin);
+                const bool leader = (__ffs(peers) - 1) == lane;
+                if (COUNT) {
+                    if (leader) atomicAdd(&hist[bin], (unsigned long long)__popc(peers));
+                } else {
+                    const unsigned int low = __reduce_add_sync(peers, (unsigned int)(mass & 0xFFFFFull));
+                    const unsigned int high = __reduce_add_sync(peers, (unsigned int)(mass >> 20));
+                    if (leader) {
+                        atomicAdd(&hist[bin], ((unsigned long long)high << 20) + low);
+                        atomicAdd(&members[bin], (unsigned int)__popc(peers));
+                    }
+                }
+            }
+          }
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned long long run = 0ull;
-            int chosen = -1, lowest = 0;
-            for (int b = 255; b >= 0; --b) {
-                if (hist[b] == 0ull) continue;
-                lowest = b;
-                if (run + hist[b] >= remaining) { chosen = b; break; }
-                run += hist[b];
+        if (threadIdx.x < 32) {
+            // Warp 0 finds the bin in which the running total, from bin 255 downwards, reaches `remaining`: lane l owns
+            // bins 255 - 8l down to 248 - 8l (one thread walking all 256 bins took 4 us a pass).
+            unsigned long long mine[8], own = 0ull;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { mine[j] = hist[255 - 8 * lane - j]; own += mine[j]; }
+            unsigned long long upto = own;                               // lanes 0..lane, i.e. the higher bins and these
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1) {
+                const unsigned long long above = __shfl_up_sync(0xffffffffu, upto, offset);
+                if (lane >= offset) upto += above;
             }
-            if (chosen < 0) {
+            const unsigned int reached = __ballot_sync(0xffffffffu, own > 0ull && upto >= remaining);
+            const unsigned int holders = __ballot_sync(0xffffffffu, own > 0ull);
+            if (reached) {
+                if (lane == __ffs(reached) - 1) {
+                    unsigned long long run = upto - own;                 // the total of the bins above this lane's
+                    for (int j = 0; j < 8; ++j) {
+                        if (mine[j] == 0ull) continue;
+                        if (run + mine[j] >= remaining) {
+                            const int chosen = 255 - 8 * lane - j;
+                            shared_pick[0] = (unsigned long long)chosen;
+                            shared_pick[1] = remaining - run;
+                            shared_pick[2] = COUNT ? mine[j] : (unsigned long long)members[chosen];    // elements in that bin
+                            break;
+                        }
+                        run += mine[j];
+                    }
+                }
+            } else if (lane == (holders ? 31 - __clz(holders) : 0)) {
                 // Cannot happen with integer masses (each level's bins add up to the bin
                 // chosen above); if it did, keep everything down to the lowest key.
-                chosen = lowest;
+                int lowest = 255 - 8 * lane;
+                for (int j = 0; j < 8; ++j) if (mine[j] != 0ull) lowest = 255 - 8 * lane - j;
+                shared_pick[0] = (unsigned long long)lowest;
                 shared_pick[1] = hist[lowest];
-            } else {
-                shared_pick[1] = remaining - run;
+                shared_pick[2] = COUNT ? hist[lowest] : (unsigned long long)members[lowest];
             }
-            shared_pick[0] = (unsigned long long)chosen;
         }
         __syncthreads();
         prefix |= shared_pick[0] << shift;
         remaining = shared_pick[1];
+        const bool alone = shared_pick[2] == 1ull;
         __syncthreads();
+        if (shift == 32 && alone) break;
     }
     return prefix;
 }
@@ -176,30 +246,41 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
               float top_p, unsigned long long seed, const int* __restrict__ streams,
               const int* __restrict__ counters, int* __restrict__ flag) {
     __shared__ unsigned long long hist[256];
-    __shared__ unsigned long long pick[2];
-    __shared__ unsigned long long chunk_sum[SAMPLE_THREADS];
+    __shared__ unsigned int members[256];
+    __shared__ unsigned long long pick[3];
+    __shared__ unsigned long long warp_total[SAMPLE_WARPS];
     __shared__ float scratch[33];
     __shared__ int bad_flag;
     pdl_launch_dependents();
     pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) bad_flag = 0;
     __syncthreads();
 
     // maximum of the scaled logits (and the finite check)
     float local_max = -INFINITY;
     bool bad = false;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i] / temperature;
-        if (!isfinite(v)) bad = true;
-        local_max = fmaxf(local_max, v);
+    // (four loads on their way per thread: the row comes from L2 the first time)
+    for (int i0 = threadIdx.x; i0 < vocab; i0 += 4 * SAMPLE_THREADS) {
+        float x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) x[u] = i0 + u * SAMPLE_THREADS < vocab ? row[i0 + u * SAMPLE_THREADS] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i0 + u * SAMPLE_THREADS < vocab) {
+                const float v = x[u] / temperature;
+                if (!isfinite(v)) bad = true;
+                local_max = fmaxf(local_max, v);
+            }
+        }
     }
     if (bad) bad_flag = 1;
     local_max = warp_max(local_max);
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = local_max;
+    if (lane == 0) scratch[warp] = local_max;
     __syncthreads();
     if (threadIdx.x < 32) {
-        float m = threadIdx.x < (blockDim.x >> 5) ? scratch[threadIdx.x] : -INFINITY;
+        float m = threadIdx.x < SAMPLE_WARPS ? scratch[threadIdx.x] : -INFINITY;
         m = warp_max(m);
         if (threadIdx.x == 0) scratch[32] = m;
     }
@@ -212,72 +293,78 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
 
     unsigned long long floor_key = 0ull;
     if (top_k > 0 && top_k < vocab)
-        floor_key = radix_select<true>(row, vocab, temperature, max_value, 0ull, (unsigned long long)top_k, hist, pick);
+        floor_key = radix_select<true>(row, vocab, temperature, max_value, 0ull, (unsigned long long)top_k, hist, members, pick);
 
-    // total mass of what is allowed so far
-    auto total_mass = [&](unsigned long long floor) {
+    // A warp owns a stretch of the row and each of its lanes a run of consecutive elements in it (a lane's loads walk
+    // along cache lines that stay in L1).  A lane keeps the mass of what is allowed in its run; the warp's total goes
+    // to warp_total.  Integer masses: the totals do not depend on who adds what.
+    const int per_lane = ((vocab + SAMPLE_WARPS - 1) / SAMPLE_WARPS + 31) / 32;
+    const int begin = min(vocab, (warp * 32 + lane) * per_lane), end = min(vocab, begin + per_lane);
+    auto lane_mass = [&](unsigned long long floor) {
         unsigned long long local = 0ull;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        for (int i = begin; i < end; ++i) {
             const float v = row[i] / temperature;
             if (sort_key(v, i) >= floor) local += fixed_mass(v, max_value);
         }
+        const unsigned long long total = warp_sum_u64(local);
+        __syncthreads();                           // (whoever still reads the totals of a round before has done so)
+        if (lane == 0) warp_total[warp] = total;
         __syncthreads();
-        chunk_sum[threadIdx.x] = local;
-        __syncthreads();
-        for (int stride = SAMPLE_THREADS / 2; stride > 0; stride >>= 1) {
-            if (threadIdx.x < stride) chunk_sum[threadIdx.x] += chunk_sum[threadIdx.x + stride];
-            __syncthreads();
-        }
-        const unsigned long long total = chunk_sum[0];
-        __syncthreads();
-        return total;
+        return local;
     };
 
     if (top_p < 1.0f) {
-        const unsigned long long total = total_mass(floor_key);
+        lane_mass(floor_key);
+        unsigned long long total = 0ull;
+        for (int w = 0; w < SAMPLE_WARPS; ++w) total += warp_total[w];
         unsigned long long target = (unsigned long long)((double)top_p * (double)total);
         if (target < 1ull) target = 1ull;
-        floor_key = radix_select<false>(row, vocab, temperature, max_value, floor_key, target, hist, pick);
+        floor_key = radix_select<false>(row, vocab, temperature, max_value, floor_key, target, hist, members, pick);
     }
 
-    // draw: inverse CDF over the survivors in index order, contiguous chunk per thread
-    const int per_thread = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-    const int begin = min(vocab, (int)threadIdx.x * per_thread), end = min(vocab, begin + per_thread);
-    unsigned long long mine = 0ull;
-    for (int i = begin; i < end; ++i) {
-        const float v = row[i] / temperature;
-        if (sort_key(v, i) >= floor_key) mine += fixed_mass(v, max_value);
-    }
-    chunk_sum[threadIdx.x] = mine;
-    __syncthreads();
+    // draw: the inverse of the cumulative masses of the survivors in index order: the warp, then the lane, then the
+    // element in whose mass the drawn number falls
+    const unsigned long long mine = lane_mass(floor_key);
     if (threadIdx.x == 0) {
         unsigned long long total = 0ull;
-        for (int t = 0; t < SAMPLE_THREADS; ++t) total += chunk_sum[t];
+        for (int w = 0; w < SAMPLE_WARPS; ++w) total += warp_total[w];
         const uint32_t r = philox_first_word(seed, (uint32_t)streams[blockIdx.x], (uint32_t)counters[blockIdx.x]);
         // target in [0, total): floor(total * r / 2^32) with a 96-bit product
-        const unsigned long long hi = __umul64hi(total, (unsigned long long)r << 32);
-        unsigned long long target = hi;
+        const unsigned long long target = __umul64hi(total, (unsigned long long)r << 32);
         unsigned long long run = 0ull;
-        int owner = SAMPLE_THREADS - 1;
-        for (int t = 0; t < SAMPLE_THREADS; ++t) {
-            if (target < run + chunk_sum[t]) { owner = t; break; }
-            run += chunk_sum[t];
+        int owner = SAMPLE_WARPS - 1;
+        for (int w = 0; w < SAMPLE_WARPS; ++w) {
+            if (target < run + warp_total[w]) { owner = w; break; }
+            run += warp_total[w];
         }
         pick[0] = (unsigned long long)owner;
         pick[1] = target - run;
     }
     __syncthreads();
-    if ((int)pick[0] == (int)threadIdx.x) {
-        unsigned long long left = pick[1], run = 0ull;
-        int chosen = -1, last_allowed = -1;
-        for (int i = begin; i < end; ++i) {
-            const float v = row[i] / temperature;
-            if (sort_key(v, i) < floor_key) continue;
-            last_allowed = i;
-            run += fixed_mass(v, max_value);
-            if (left < run) { chosen = i; break; }
+    if ((int)pick[0] == warp) {
+        unsigned long long upto = mine;                                  // inclusive sum over lanes 0..lane
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1) {
+            const unsigned long long below = __shfl_up_sync(0xffffffffu, upto, offset);
+            if (lane >= offset) upto += below;
         }
-        out[blockIdx.x] = chosen >= 0 ? chosen : max(last_allowed, 0);
+        const unsigned long long left = pick[1];
+        const unsigned int crossed = __ballot_sync(0xffffffffu, mine > 0ull && left < upto);
+        const unsigned int holders = __ballot_sync(0xffffffffu, mine > 0ull);
+        // (no lane crossed: cannot happen with integer masses; the last lane that holds anything then gives its last element)
+        const int owner_lane = crossed ? __ffs(crossed) - 1 : (holders ? 31 - __clz(holders) : 0);
+        if (lane == owner_lane) {
+            unsigned long long remaining = crossed ? left - (upto - mine) : ~0ull, run = 0ull;
+            int chosen = -1, last_allowed = -1;
+            for (int i = begin; i < end; ++i) {
+                const float v = row[i] / temperature;
+                if (sort_key(v, i) < floor_key) continue;
+                last_allowed = i;
+                run += fixed_mass(v, max_value);
+                if (remaining < run) { chosen = i; break; }
+            }
+            out[blockIdx.x] = chosen >= 0 ? chosen : max(last_allowed, 0);
+        }
     }
 }
 
