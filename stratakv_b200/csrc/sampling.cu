@@ -141,55 +141,99 @@ __device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v)
 // integers below 2^41, added as two halves of 20 bits so that the warp's 32-bit reduction serves.  When all 32 bits
 // of the value are fixed and one element alone has that value there is no tie for the index bits to break: the last
 // four passes are left out and the key's index bits stay zero, which keeps the same elements.
+constexpr int SAMPLE_CANDIDATES = 4096;            // indices a block keeps once few enough elements are left in play
+
 template <bool COUNT>
-__device__ unsigned long long radix_select(const float* __restrict__ row, int vocab, float inv_scale_div,
+__device__ unsigned long long radix_select(const float* __restrict__ row, const float* scaled, int vocab, float inv_scale_div,
                                            float max_value, unsigned long long floor_key,
                                            unsigned long long target, unsigned long long* hist, unsigned int* members,
-                                           unsigned long long* shared_pick) {
-    const int lane = threadIdx.x & 31;
+                                           unsigned long long* warp_hist, unsigned int* warp_members, int* candidates,
+                                           unsigned long long* shared_pick, unsigned long long in_play) {
+    // in_play: at most this many elements have a key >= floor_key (all of them: ~0)
+    // warp_hist [warps][256], warp_members [warps][256]: a warp adds to its own histogram with plain reads and writes
+    // (its leaders of one round hold different bins), and the histograms are added up after the walk: atomic additions
+    // of sixteen warps to the two or three bins that a pass over the high bits fills cost more than the walk itself.
+    // Only the elements of the bin that a pass chose are in play in the next one.  Once they are at most
+    // SAMPLE_CANDIDATES, the next walk over the row writes their indices down (candidates; shared_pick[3] counts them),
+    // and the passes after it walk that list instead of the row.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned long long* my_hist = warp_hist + warp * 256;
+    unsigned int* my_members = warp_members + warp * 256;
     unsigned long long prefix = 0ull, remaining = target;
+    int listed = -1;                                   // how many indices the list holds (-1: none yet)
     for (int shift = 56; shift >= 0; shift -= 8) {
-        for (int b = threadIdx.x; b < 256; b += blockDim.x) { hist[b] = 0ull; members[b] = 0u; }
+        for (int b = threadIdx.x; b < 256 * SAMPLE_WARPS; b += blockDim.x) { warp_hist[b] = 0ull; warp_members[b] = 0u; }
+        const bool collect = listed < 0 && in_play <= (unsigned long long)SAMPLE_CANDIDATES;
+        if (threadIdx.x == 0) shared_pick[3] = 0ull;
         __syncthreads();
         const unsigned long long high_mask = shift == 56 ? 0ull : (~0ull << (shift + 8));
-        for (int base4 = (int)threadIdx.x - lane; base4 < vocab; base4 += 4 * SAMPLE_THREADS) {   // the same trips for a warp's lanes
-          float x[4];                                                    // four loads on their way
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-              const int i = base4 + u * SAMPLE_THREADS + lane;
-              x[u] = i < vocab ? row[i] : 0.0f;
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int base = base4 + u * SAMPLE_THREADS;
-            if (base >= vocab) break;
-            const int i = base + lane;
+        // one element a lane: `live` lanes bring an element (index i, scaled value v) that may or may not be in play
+        auto account = [&](bool live, int i, float v) {
             bool valid = false;
             int bin = 0;
             unsigned long long mass = 0ull;
-            if (i < vocab) {
-                const float v = x[u] / inv_scale_div;
+            if (live) {
                 const unsigned long long key = sort_key(v, i);
                 valid = key >= floor_key && (key & high_mask) == prefix;
                 bin = (int)((key >> shift) & 0xFFull);
                 if (!COUNT && valid) mass = fixed_mass(v, max_value);
             }
             const unsigned int voters = __ballot_sync(0xffffffffu, valid);
+            if (voters == 0u) return;
+            if (collect) {
+                int slot = 0;
+                if (lane == __ffs(voters) - 1) slot = (int)atomicAdd(&shared_pick[3], (unsigned long long)__popc(voters));
+                slot = __shfl_sync(0xffffffffu, slot, __ffs(voters) - 1);
+                if (valid) candidates[slot + __popc(voters & ((1u << lane) - 1u))] = i;
+            }
             if (valid) {
                 const unsigned int peers = __match_any_sync(voters, bin);
                 const bool leader = (__ffs(peers) - 1) == lane;
                 if (COUNT) {
-                    if (leader) atomicAdd(&hist[bin], (unsigned long long)__popc(peers));
+                    if (leader) my_hist[bin] += (unsigned long long)__popc(peers);
                 } else {
                     const unsigned int low = __reduce_add_sync(peers, (unsigned int)(mass & 0xFFFFFull));
                     const unsigned int high = __reduce_add_sync(peers, (unsigned int)(mass >> 20));
                     if (leader) {
-                        atomicAdd(&hist[bin], ((unsigned long long)high << 20) + low);
-                        atomicAdd(&members[bin], (unsigned int)__popc(peers));
+                        my_hist[bin] += ((unsigned long long)high << 20) + low;
+                        my_members[bin] += (unsigned int)__popc(peers);
                     }
                 }
             }
-          }
+            __syncwarp();                          // (a round's writes before the next round's reads of the same bins)
+        };
+        if (listed >= 0) {
+            for (int base = (int)threadIdx.x - lane; base < listed; base += SAMPLE_THREADS) {
+                const int c = base + lane;
+                const bool live = c < listed;
+                const int i = live ? candidates[c] : 0;
+                const float v = live ? (scaled ? scaled[i] : row[i] / inv_scale_div) : 0.0f;
+                account(live, i, v);
+            }
+        } else {
+            for (int base4 = (int)threadIdx.x - lane; base4 < vocab; base4 += 4 * SAMPLE_THREADS) {   // the same trips for a warp's lanes
+                float x[4];                                              // four loads on their way
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = base4 + u * SAMPLE_THREADS + lane;
+                    x[u] = i < vocab ? (scaled ? scaled[i] : row[i]) : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int base = base4 + u * SAMPLE_THREADS;
+                    if (base >= vocab) break;
+                    const int i = base + lane;
+                    account(i < vocab, i, scaled ? x[u] : x[u] / inv_scale_div);
+                }
+            }
+        }
+        __syncthreads();
+        for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+            unsigned long long total = 0ull;
+            unsigned int count = 0u;
+            for (int w = 0; w < SAMPLE_WARPS; ++w) { total += warp_hist[w * 256 + b]; count += warp_members[w * 256 + b]; }
+            hist[b] = total;
+            members[b] = count;
         }
         __syncthreads();
         if (threadIdx.x < 32) {
@@ -234,9 +278,10 @@ __device__ unsigned long long radix_select(const float* __restrict__ row, int vo
         __syncthreads();
         prefix |= shared_pick[0] << shift;
         remaining = shared_pick[1];
-        const bool alone = shared_pick[2] == 1ull;
+        in_play = shared_pick[2];
+        if (collect) listed = (int)shared_pick[3];
         __syncthreads();
-        if (shift == 32 && alone) break;
+        if (shift == 32 && in_play == 1ull) break;
     }
     return prefix;
 }
@@ -244,10 +289,17 @@ __device__ unsigned long long radix_select(const float* __restrict__ row, int vo
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, float temperature, int top_k,
               float top_p, unsigned long long seed, const int* __restrict__ streams,
-              const int* __restrict__ counters, int* __restrict__ flag) {
+              const int* __restrict__ counters, int* __restrict__ flag, int staged) {
+    // `staged`: the row divided by the temperature is kept in (dynamic) shared memory after the first walk, and the
+    // later walks read it there; rows too long for that are read and divided again each time, with the same results
+    extern __shared__ __align__(16) unsigned char sample_smem[];
+    unsigned long long* warp_hist = (unsigned long long*)sample_smem;             // [warps][256]
+    unsigned int* warp_members = (unsigned int*)(warp_hist + SAMPLE_WARPS * 256);  // [warps][256]
+    int* candidates = (int*)(warp_members + SAMPLE_WARPS * 256);                  // [SAMPLE_CANDIDATES]
+    float* scaled = staged ? (float*)(candidates + SAMPLE_CANDIDATES) : nullptr;
     __shared__ unsigned long long hist[256];
     __shared__ unsigned int members[256];
-    __shared__ unsigned long long pick[3];
+    __shared__ unsigned long long pick[4];
     __shared__ unsigned long long warp_total[SAMPLE_WARPS];
     __shared__ float scratch[33];
     __shared__ int bad_flag;
@@ -270,6 +322,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
         for (int u = 0; u < 4; ++u) {
             if (i0 + u * SAMPLE_THREADS < vocab) {
                 const float v = x[u] / temperature;
+                if (scaled) scaled[i0 + u * SAMPLE_THREADS] = v;
                 if (!isfinite(v)) bad = true;
                 local_max = fmaxf(local_max, v);
             }
@@ -293,7 +346,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
 
     unsigned long long floor_key = 0ull;
     if (top_k > 0 && top_k < vocab)
-        floor_key = radix_select<true>(row, vocab, temperature, max_value, 0ull, (unsigned long long)top_k, hist, members, pick);
+        floor_key = radix_select<true>(row, scaled, vocab, temperature, max_value, 0ull, (unsigned long long)top_k, hist, members, warp_hist,
+                                       warp_members, candidates, pick, ~0ull);
 
     // A warp owns a stretch of the row and each of its lanes a run of consecutive elements in it (a lane's loads walk
     // along cache lines that stay in L1).  A lane keeps the mass of what is allowed in its run; the warp's total goes
@@ -303,7 +357,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     auto lane_mass = [&](unsigned long long floor) {
         unsigned long long local = 0ull;
         for (int i = begin; i < end; ++i) {
-            const float v = row[i] / temperature;
+            const float v = scaled ? scaled[i] : row[i] / temperature;
             if (sort_key(v, i) >= floor) local += fixed_mass(v, max_value);
         }
         const unsigned long long total = warp_sum_u64(local);
@@ -319,7 +373,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
         for (int w = 0; w < SAMPLE_WARPS; ++w) total += warp_total[w];
         unsigned long long target = (unsigned long long)((double)top_p * (double)total);
         if (target < 1ull) target = 1ull;
-        floor_key = radix_select<false>(row, vocab, temperature, max_value, floor_key, target, hist, members, pick);
+        floor_key = radix_select<false>(row, scaled, vocab, temperature, max_value, floor_key, target, hist, members, warp_hist,
+                                        warp_members, candidates, pick, floor_key ? (unsigned long long)top_k : ~0ull);
     }
 
     // draw: the inverse of the cumulative masses of the survivors in index order: the warp, then the lane, then the
@@ -357,7 +412,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
             unsigned long long remaining = crossed ? left - (upto - mine) : ~0ull, run = 0ull;
             int chosen = -1, last_allowed = -1;
             for (int i = begin; i < end; ++i) {
-                const float v = row[i] / temperature;
+                const float v = scaled ? scaled[i] : row[i] / temperature;
                 if (sort_key(v, i) < floor_key) continue;
                 last_allowed = i;
                 run += fixed_mass(v, max_value);
@@ -379,6 +434,18 @@ SKV_EXPORT int skv_sample(const float* logits, int* out, int rows, int vocab, fl
         return fail("skv_sample", "temperature must be positive and finite (0 is greedy: use skv_argmax)");
     if (top_k < 0) return fail("skv_sample", "top_k must be non-negative");
     if (!(top_p > 0.0f) || top_p > 1.0f) return fail("skv_sample", "top_p must be in (0, 1]");
-    return launch_pdl("skv_sample", sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, logits, out, vocab,
-                      temperature, top_k, top_p, (unsigned long long)seed, streams, counters, flag);
+    // a row of up to 38,912 logits is kept in shared memory between the kernel's walks over it
+    const size_t row_bytes = (size_t)vocab * sizeof(float);
+    const size_t histograms = (size_t)SAMPLE_WARPS * 256 * (sizeof(unsigned long long) + sizeof(unsigned int)) +
+                              (size_t)SAMPLE_CANDIDATES * sizeof(int);      // 48 KB of histograms and 16 KB of indices
+    const int staged = row_bytes <= 152 * 1024 ? 1 : 0;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t status = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                        (int)(histograms + 152 * 1024));
+        if (status != cudaSuccess) return fail("skv_sample", cudaGetErrorString(status));
+        configured = true;
+    }
+    return launch_pdl("skv_sample", sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), histograms + (staged ? row_bytes : 0), stream, logits, out,
+                      vocab, temperature, top_k, top_p, (unsigned long long)seed, streams, counters, flag, staged);
 }
