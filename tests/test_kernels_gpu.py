@@ -88,6 +88,8 @@ def pack_gate_up(w):
                                    (33, 80, 176), (64, 512, 512), (70, 130, 520), (200, 64, 72),
                                    (32, 2048, 5632), (64, 2560, 2048), (100, 1000, 1032), (128, 384, 4096),
                                    (5, 12288, 264),           # 768 row tiles of the small-step kernel
+                                   (20, 48, 64), (40, 256, 192), (64, 256, 1280), (128, 512, 1344),   # two chunks a copy: one
+                                                              # chunk in all, an odd count, parts of K of five and of seven chunks
                                    (20, 19000, 136), (64, 19072, 520), (100, 20000, 264)])   # more 128-row tiles than
                                                               # SMs: the swapped kernel's shallow rings, two blocks an SM
 def test_linear_store_and_add(dtype, M, N, K):
