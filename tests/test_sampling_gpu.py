@@ -73,3 +73,32 @@ def test_non_finite_logits_raise_the_flag():
     zeros = torch.zeros(2, dtype=torch.int32, device="cuda")
     k.sample(logits, out, 1.0, 0, 1.0, 0, zeros, zeros, flag)
     assert int(flag) & 2
+
+
+def test_long_rows_and_ties_take_the_other_paths_of_the_kernel():
+    """Rows longer than the kernel keeps in shared memory are read again on every walk; many equal values make the
+    passes over the index bits run; a top-k above what the list of elements in play holds keeps it from being made."""
+    vocab = 50000
+    rng = np.random.default_rng(5)
+    logits = (-30.0 + 0.01 * rng.standard_normal(vocab)).astype(np.float32)
+    logits[[7, 31000, 49999]] = [3.0, 2.5, 2.0]
+    n = 6000
+    drawn = draw(logits, n, 1.0, 3, 1.0)
+    assert set(drawn) == {7, 31000, 49999}
+    expected = np.exp([3.0, 2.5, 2.0]) / np.exp([3.0, 2.5, 2.0]).sum()
+    counts = np.array([(drawn == i).sum() for i in (7, 31000, 49999)])
+    assert (np.abs(counts - n * expected) < 5 * np.sqrt(n * expected * (1 - expected))).all()
+    assert set(draw(logits, 500, 1.0, 0, 0.3)) == {7}                    # its share is 0.51: it crosses 0.3 alone
+    assert set(draw(logits, 2000, 1.0, 0, 0.6)) == {7, 31000}            # 0.51 + 0.31 crosses 0.6
+    # all values equal: the k lowest indices stay, whatever k
+    flat = np.zeros(vocab, dtype=np.float32)
+    assert set(draw(flat, 3000, 1.0, 5, 1.0)) == {0, 1, 2, 3, 4}
+    assert set(draw(flat, 400, 0.7, 1, 1.0)) == {0}
+    # more survivors than the list of elements in play holds
+    slope = (-1e-4 * np.arange(vocab)).astype(np.float32)
+    many = draw(slope, 4000, 1.0, 6000, 1.0)
+    assert many.max() < 6000 and many.min() < 300 and (many > 3000).sum() > 1000
+    # and the same three tokens on a row that does fit
+    short = logits[:32000].copy()
+    short[[7, 31000, 31999]] = [3.0, 2.5, 2.0]
+    assert set(draw(short, 3000, 1.0, 3, 1.0)) == {7, 31000, 31999}
