@@ -169,6 +169,27 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
     return __fdividef(g, 1.0f + __expf(-z));
 }
 
+// Which tile of the output a block's t-th tile is.  Row tiles run fastest, so that blocks which run together share a
+// W tile; but with very many tokens the A tiles of one sweep over the rows no longer fit in L2 (39,000 tokens x 4,096
+// x 2 bytes are 320 MB) and every column of tiles would fetch A from memory again.  So the rows are walked in bands:
+// within a band of `band` row tiles, columns outside, rows inside; a band's A rows (at most about 40 MB, a third of
+// L2: 39,294 tokens of the Llama-3-8B shape took 590 ms in one sweep, 518 / 481 / 460 / 468 / 496 ms with bands of
+// 96 / 64 / 40 / 24 / 12 MB) stay in L2 while W, which is smaller, streams past once per band.
+__device__ __forceinline__ void tile_coordinates(int tile, int m_tiles, int n_tiles, int band, int& m_tile, int& n_tile) {
+    const int per_band = band * n_tiles;
+    const int b = tile / per_band, within = tile - b * per_band;
+    const int rows_here = min(band, m_tiles - b * band);
+    n_tile = within / rows_here;
+    m_tile = b * band + (within - n_tile * rows_here);
+}
+
+// How many row tiles of `tile_rows` rows make a band (see tile_coordinates)
+__host__ __device__ inline int tile_band(int tile_rows, int K) {
+    const long long bytes_per_tile = (long long)tile_rows * K * 2;
+    const long long band = (40ll << 20) / (bytes_per_tile > 0 ? bytes_per_tile : 1);
+    return (int)(band < 1 ? 1 : (band > (1 << 20) ? (1 << 20) : band));
+}
+
 // The epilogue of one output tile for one of the four epilogue warps: reads the warp's quarter of the
 // accumulator (TMEM lanes 32*quarter .., one output row per thread) and stores it in the mode asked for.
 template <int BN>
@@ -445,6 +466,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int k_iters = (K + TC_BK - 1) / TC_BK;
     const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
+    const int band = tile_band(TC_BM, K);
     const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
     const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
 
@@ -473,7 +495,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         int it = 0;                               // k iterations issued so far, over all tiles
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            int m_tile, n_tile;
+            tile_coordinates(tile, m_tiles, n_tiles, band, m_tile, n_tile);
+            const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
             for (int i = 0; i < k_iters; ++i, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, flag);
@@ -535,7 +559,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, flag);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * BN;
+            int m_tile, n_tile;
+            tile_coordinates(tile, m_tiles, n_tiles, band, m_tile, n_tile);
+            const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
             if (mode == TC_MODE_QKV_ROPE) {
                 if constexpr (BN % 128 == 0)
                     epilogue_tile_rope<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, rope,
@@ -632,6 +658,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int k_iters = (K + TC_BK - 1) / TC_BK;
     const int m_tiles = (M + 2 * TC_BM - 1) / (2 * TC_BM), n_tiles = (N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
+    const int band = tile_band(2 * TC_BM, K);
     const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
     const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
 
@@ -663,8 +690,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         int it = 0;
         const uint32_t first_full0 = cluster_address(full0, 0);
         for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
-            const int m0 = (tile % m_tiles) * 2 * TC_BM + (int)rank * TC_BM;
-            const int w0 = (tile / m_tiles) * BN + (int)rank * (BN / 2);
+            int m_tile, n_tile;
+            tile_coordinates(tile, m_tiles, n_tiles, band, m_tile, n_tile);
+            const int m0 = m_tile * 2 * TC_BM + (int)rank * TC_BM;
+            const int w0 = n_tile * BN + (int)rank * (BN / 2);
             for (int i = 0; i < k_iters; ++i, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, flag);
@@ -726,7 +755,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, flag);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int m0 = (tile % m_tiles) * 2 * TC_BM + (int)rank * TC_BM, n0 = (tile / m_tiles) * BN;
+            int m_tile, n_tile;
+            tile_coordinates(tile, m_tiles, n_tiles, band, m_tile, n_tile);
+            const int m0 = m_tile * 2 * TC_BM + (int)rank * TC_BM, n0 = n_tile * BN;
             if (mode == TC_MODE_QKV_ROPE) {
                 epilogue_tile_rope<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, rope,
                                        M, N, m0, n0);

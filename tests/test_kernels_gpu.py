@@ -177,6 +177,8 @@ def _products(a, w, chunk=512):
                                                      # block has 104 live rows in the last tile), N and K at once
     (1100, 2560, 6000, "store gated"),               # pairs: the second block of the last row tile has no live row
     (1500, 2501, 5208, "store_f32 store add"),       # pairs whose rows the threads store themselves
+    (7000, 512, 5632, "store add"),                  # pairs: so many rows that they are walked in two bands (14 + 14 row tiles)
+    (5000, 256, 8192, "store_f32 add"),              # 128-wide tiles in two bands (20 + 20 row tiles)
 ])
 def test_linear_tiled_tensor_memory_kernel_at_model_sizes(M, N, K, modes):
     """tests/gemv_smoke.cu:329-357 takes the reference's kernels to the model's shapes with a bound from
@@ -231,9 +233,11 @@ def test_the_shapes_of_these_tests_reach_every_tensor_memory_kernel():
     assert k.linear_form(2048, 2560, 2048, ops.MODE_QKV_ROPE) == "tile_256"
     assert k.linear_form(2048, 11264, 520, ops.MODE_GATED) == "tile_256"            # a short inner size: no pair
     assert k.linear_form(2048, 2048, 2048, ops.MODE_ADD_F32) == "tile_256"      # one short tile a block: no pair
+    assert k.linear_form(5000, 256, 8192, ops.MODE_STORE_F32) == "tile_128"
     for M, N, K, mode in [(2048, 11264, 2048, ops.MODE_GATED), (2048, 2048, 5632, ops.MODE_ADD_F32),
                           (1000, 4112, 5200, ops.MODE_GATED), (1000, 4112, 5200, ops.MODE_STORE),
                           (1100, 2560, 6000, ops.MODE_STORE), (1500, 2501, 5208, ops.MODE_ADD_F32),
+                          (7000, 512, 5632, ops.MODE_ADD_F32),
                           (1000, 3072, 5120, ops.MODE_QKV_ROPE), (900, 3136, 5200, ops.MODE_QKV_ROPE)]:
         assert k.linear_form(M, N, K, mode) == "pair_256", (M, N, K, mode)
 
